@@ -1,0 +1,195 @@
+/*
+ * C ABI of the B200 (sm_100a) attention hot path behind the MindIE-SD layer API.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues its kernels on the CUDA
+ * stream it is given (a cudaStream_t passed as void*; NULL = the default stream) and returns
+ * without synchronising.  Return value: 0 = enqueued; negative = invalid argument
+ * (MINDIESD_E_*); positive = a cudaError_t raised by the launch.  No exception crosses this
+ * boundary and inputs are never written.  Unless stated otherwise an entry point allocates
+ * nothing; scratch memory is supplied by the caller.
+ *
+ * The reference interface each entry point stands in for is cited by its path inside the
+ * MindIE-SD source tree.
+ */
+#ifndef MINDIESD_B200_H_
+#define MINDIESD_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MINDIESD_B200_ABI_VERSION 1
+
+enum {
+    MINDIESD_OK = 0,
+    MINDIESD_E_NULL = -1,     /* a required pointer is NULL                                  */
+    MINDIESD_E_SHAPE = -2,    /* unsupported size (head_dim, block size, block count ...)    */
+    MINDIESD_E_DTYPE = -3,    /* unsupported element type combination                        */
+    MINDIESD_E_STRIDE = -4,   /* stride/pointer not aligned as the TMA engine requires       */
+    MINDIESD_E_VALUE = -5,    /* scalar argument out of range                                */
+    MINDIESD_E_DRIVER = -6,   /* the CUDA driver refused a tensor-map or attribute request   */
+    MINDIESD_E_CAPACITY = -7  /* size exceeds a fixed capacity of the entry point            */
+};
+
+enum { MINDIESD_BF16 = 0, MINDIESD_FP16 = 1, MINDIESD_FP32 = 2, MINDIESD_E4M3 = 3 };
+
+/* Block-sparsity source for mindiesd_attention_fwd. */
+enum {
+    MINDIESD_SPARSE_NONE = 0, /* dense                                                         */
+    MINDIESD_SPARSE_MASK = 1, /* int8 mask [B, N, q_blocks, kv_blocks], non-zero = attend      */
+    MINDIESD_SPARSE_LIST = 2  /* ascending int64 block ids [q_blocks, N, kv_blocks] + counts   */
+};
+
+/*
+ * Attention forward:  out = softmax(scale * q k^T  [restricted to kept 128x128 blocks]) v.
+ *
+ * Tensors are addressed as [batch, head, token, channel] through element strides, so BNSD,
+ * BSND and TND (batch = 1) are all expressed without copies; the channel stride is 1.
+ * q/k/v: bf16 or fp16 (in_dtype), or e4m3 with dequantisation scales (see below).
+ * out:   in_dtype, or fp32 (out_dtype = MINDIESD_FP32); for e4m3 inputs bf16/fp16/fp32.
+ * lse:   optional fp32 [B, N, seq_q] natural-log-sum-exp of the scaled scores (NULL = skip).
+ * Rows whose every block is masked produce zeros (lse = -inf).
+ *
+ * Stands in for: torch_npu.npu_prompt_flash_attention / npu_fusion_attention as called by
+ * mindiesd/layers/flash_attn/prompt_flash_attn.py:48-57 and fused_attn_score.py:48-57;
+ * aclnnLaserAttention launched by csrc/plugin/la.cpp:54-56; aclnnBlockSparseAttention launched
+ * by csrc/plugin/block_sparse_attention.cpp:97-118 (MINDIESD_SPARSE_MASK);
+ * aclnnRainFusionAttention launched by csrc/plugin/rainfusionattention.cpp:60-62
+ * (MINDIESD_SPARSE_LIST); npu_fused_infer_attention_score_v2 with quant mode 7 as called by
+ * mindiesd/quantization/layer.py:304-316 (in_dtype = MINDIESD_E4M3).
+ */
+typedef struct mindiesd_attn_args {
+    const void* q;
+    const void* k;
+    const void* v;
+    void* out;
+    float* lse;
+    int32_t batch, heads, kv_heads, seq_q, seq_kv, head_dim;
+    int64_t q_stride[3]; /* element strides of batch, head, token */
+    int64_t k_stride[3];
+    int64_t v_stride[3];
+    int64_t o_stride[3];
+    int32_t in_dtype;
+    int32_t out_dtype;
+    float scale;
+
+    int32_t sparse_mode;
+    int32_t block_size;         /* must be 128 when sparse_mode != NONE */
+    const int8_t* block_mask;   /* MASK: element strides of batch, head, q-block; kv-block stride 1 */
+    int64_t mask_stride[3];
+    const int64_t* select_idx;  /* LIST: [q_blocks, heads, kv_blocks], -1 padded, batch-invariant */
+    const int64_t* select_num;  /* LIST: [q_blocks, heads] */
+
+    /* e4m3 inputs only: real value = stored value * scale.
+       q_scale [B, N, ceil(seq_q / 128)], k_scale [B, Nkv, ceil(seq_kv / k_scale_block)],
+       v_scale [B, Nkv, head_dim] when v_scale_block == 0 (one scale per channel), else
+       [B, Nkv, ceil(seq_kv / v_scale_block)].  Scale blocks are 128, 256 or 512 tokens. */
+    const float* q_scale;
+    const float* k_scale;
+    const float* v_scale;
+    int32_t k_scale_block;
+    int32_t v_scale_block;
+} mindiesd_attn_args;
+
+int mindiesd_attention_fwd(const mindiesd_attn_args* args, void* stream);
+
+/*
+ * RainFusion token permutation of the image tokens of a (t, h, w) latent grid into 8x8 spatial
+ * windows (forward) and back (inverse = 1), text tokens moved from the front to the back
+ * (forward) or back to the front (inverse).  src/dst: [B, N, S, D] by element strides, 2-byte
+ * elements, D a multiple of 8, S = txt_len + t*h*w.  dst must not alias src.
+ *
+ * Stands in for rearrange_with_remaining / inv_rearrange_with_remaining /
+ * do_tensor_inv_rearrange (mindiesd/layers/flash_attn/sparse_flash_attn_rf_v2.py:137-196,
+ * 199-289, 321-337), _bsa_inv_rearrange and do_tensor_rearrange_only
+ * (sparse_flash_attn_rf_v3.py:22-118).
+ */
+typedef struct mindiesd_rearrange_args {
+    const void* src;
+    void* dst;
+    int32_t batch, heads, seq, head_dim;
+    int64_t src_stride[3];
+    int64_t dst_stride[3];
+    int32_t t, h, w, txt_len;
+    int32_t inverse;
+} mindiesd_rearrange_args;
+
+int mindiesd_rf_rearrange(const mindiesd_rearrange_args* args, void* stream);
+
+/*
+ * RainFusion block-mask builder.  q and k are in their ORIGINAL token order; the window
+ * permutation is applied in the index arithmetic.  Per head: mean of every 128-token block of
+ * the permuted q and k (the tail block over its real length), block scores q_mean . k_mean,
+ * keep the ceil(kv_blocks * (1 - sparsity)) largest of each row (every score equal to the
+ * smallest kept one is kept too), then force the text blocks (last ceil(txt_len/128) rows and
+ * columns) and, if protect_first_frame, the first ceil(h*w/128) rows and columns; if
+ * temporal_band >= 0 also every block pair whose frame ranges lie within that many frames.
+ * Outputs (each optional): mask int8 [B, N, qb, kb]; select_idx int64 [qb, N, kb] ascending,
+ * -1 padded, and select_num int64 [qb, N], both taken from batch 0 as the reference does.
+ * scratch: caller-supplied, at least mindiesd_rf_block_mask_scratch_bytes() bytes, 256-byte
+ * aligned; holds the pooled means between the two kernels.
+ *
+ * Stands in for avgpool + get_blockwise_mask + get_mask_index
+ * (mindiesd/layers/flash_attn/sparse_flash_attn_rf_v2.py:24-134).
+ */
+typedef struct mindiesd_mask_args {
+    const void* q;
+    const void* k;
+    int32_t batch, heads, seq, head_dim;
+    int64_t q_stride[3];
+    int64_t k_stride[3];
+    int32_t dtype; /* MINDIESD_BF16 / FP16 / FP32 */
+    int32_t t, h, w, txt_len;
+    int32_t block_size; /* 128 */
+    float sparsity;
+    float scale;
+    int32_t protect_first_frame;
+    int32_t temporal_band; /* < 0: off (the reference has no band) */
+    int8_t* mask;
+    int64_t* select_idx;
+    int64_t* select_num;
+    void* scratch;
+    size_t scratch_bytes;
+} mindiesd_mask_args;
+
+size_t mindiesd_rf_block_mask_scratch_bytes(int32_t batch, int32_t heads, int32_t seq, int32_t head_dim);
+int mindiesd_rf_block_mask(const mindiesd_mask_args* args, void* stream);
+
+/*
+ * Dynamic block quantisation to e4m3 for attention operands.  x: [B, N, S, D] bf16/fp16 by
+ * element strides.  mode 0: one scale per (row_block tokens x 128 channels) block,
+ * scale = absmax / 448 (1 where the block is all zero), scales fp32 [B, N, ceil(S/row_block)];
+ * mode 1: one scale per channel over the whole sequence, scales fp32 [B, N, D].
+ * out: e4m3 [B, N, S, D] contiguous.
+ *
+ * Stands in for torch_npu.npu_dynamic_block_quant as called by fa_block_quant_preprocess
+ * (mindiesd/layers/quant/block_quant.py:43-46).
+ */
+typedef struct mindiesd_quant_args {
+    const void* x;
+    void* out;
+    float* scales;
+    int32_t batch, heads, seq, head_dim;
+    int64_t x_stride[3];
+    int32_t dtype;
+    int32_t mode;
+    int32_t row_block; /* 128, 256 or 512 (mode 0) */
+} mindiesd_quant_args;
+
+int mindiesd_fa_block_quant(const mindiesd_quant_args* args, void* stream);
+
+/*
+ * Device status word of the current device: 0, or the code of the first bounded wait inside a
+ * kernel that gave up since the last call.  Synchronises the device; clears the word.
+ */
+int mindiesd_device_status(void);
+
+int mindiesd_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MINDIESD_B200_H_ */

@@ -1,0 +1,118 @@
+"""Builds the native libraries of this package in-tree with nvcc for sm_100a.
+
+    python mindie-sd_b200/csrc/build.py [--force] [--no-torch-ext]
+
+Outputs (next to the Python package, where its loader looks for them):
+    mindiesd/plugin/libmindiesd_b200.so    the C-ABI library (CUDA only, no torch types)
+    mindiesd/plugin/libPTAExtensionOPS.so  the torch operator library registering torch.ops.mindiesd.*
+The second keeps the file name the reference's loader opens
+(mindiesd/layers/register_ops.py:24-44 of MindIE-SD).
+"""
+from __future__ import annotations
+
+import argparse
+import concurrent.futures
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parent
+PKG = CSRC.parent / "mindiesd"
+PLUGIN = PKG / "plugin"
+OBJ = CSRC / "build"
+INCLUDE = CSRC.parent.parent / "include"
+
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+
+CABI_SOURCES = sorted(p.name for p in CSRC.glob("*.cu"))
+CABI_LIB = PLUGIN / "libmindiesd_b200.so"
+TORCH_EXT_SOURCES = ["torch_ops.cpp"]
+TORCH_EXT_LIB = PLUGIN / "libPTAExtensionOPS.so"
+
+
+def _nvcc() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found: the CUDA kernels of this package cannot be built")
+    return exe
+
+
+def _newer(target: Path, deps) -> bool:
+    if not target.exists():
+        return False
+    t = target.stat().st_mtime
+    return all(Path(d).stat().st_mtime <= t for d in deps)
+
+
+def _run(cmd):
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("command failed: %s\n%s\n%s" % (" ".join(map(str, cmd)), proc.stdout, proc.stderr))
+    return proc.stdout + proc.stderr
+
+
+def build_cabi(force: bool = False, verbose: bool = False) -> Path:
+    OBJ.mkdir(exist_ok=True)
+    PLUGIN.mkdir(exist_ok=True)
+    headers = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h"))
+    sources = sorted(p.name for p in CSRC.glob("*.cu"))
+    objs, jobs = [], []
+    for src in sources:
+        obj = OBJ / (src + ".o")
+        objs.append(obj)
+        if force or not _newer(obj, [CSRC / src] + headers):
+            cmd = [_nvcc()] + ARCH_FLAGS + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
+                  ["-I", str(INCLUDE), "-c", str(CSRC / src), "-o", str(obj)]
+            jobs.append(cmd)
+    if jobs:
+        with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
+            for out in pool.map(_run, jobs):
+                if verbose and out.strip():
+                    print(out)
+    if force or jobs or not _newer(CABI_LIB, objs):
+        _run([_nvcc()] + ARCH_FLAGS + ["-shared", "-cudart", "shared", "-o", str(CABI_LIB)] + [str(o) for o in objs] +
+             ["-Xlinker", "-rpath,/usr/local/cuda/lib64"])
+    return CABI_LIB
+
+
+def build_torch_ext(force: bool = False) -> Path:
+    import torch
+    from torch.utils import cpp_extension
+
+    srcs = [CSRC / s for s in TORCH_EXT_SOURCES]
+    if not force and _newer(TORCH_EXT_LIB, srcs + [CABI_LIB] + list(INCLUDE.glob("*.h"))):
+        return TORCH_EXT_LIB
+    inc = []
+    for d in cpp_extension.include_paths("cuda"):
+        inc += ["-I", d]
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    cmd = [_nvcc()] + ARCH_FLAGS + ["-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared",
+                                    "-D_GLIBCXX_USE_CXX11_ABI=%d" % abi, "-DTORCH_EXTENSION_NAME=mindiesd_b200_ops",
+                                    "-I", str(INCLUDE)] + inc + \
+          [str(s) for s in srcs] + ["-o", str(TORCH_EXT_LIB), "-L", str(PLUGIN), "-lmindiesd_b200",
+                                    "-L", torch_lib, "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda", "-lc10_cuda",
+                                    "-Xlinker", "-rpath,$ORIGIN", "-Xlinker", "-rpath," + torch_lib]
+    _run(cmd)
+    return TORCH_EXT_LIB
+
+
+def build_all(force: bool = False, torch_ext: bool = True, verbose: bool = False):
+    libs = [build_cabi(force, verbose)]
+    if torch_ext and all((CSRC / s).exists() for s in TORCH_EXT_SOURCES):
+        libs.append(build_torch_ext(force))
+    return libs
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--no-torch-ext", action="store_true")
+    ap.add_argument("-v", "--verbose", action="store_true")
+    a = ap.parse_args()
+    for lib in build_all(a.force, not a.no_torch_ext, a.verbose):
+        print(lib)
+    sys.exit(0)

@@ -1,0 +1,525 @@
+// Flash-attention forward for sm_100a: tcgen05 MMA into tensor memory, TMA-staged operands,
+// warp-specialised roles, online softmax.  One kernel serves dense and block-sparse attention
+// (bf16 / fp16 operands) and the e4m3-quantised variant.
+//
+// Work decomposition.  One CTA owns a pair of 128-row query tiles of one (batch, head) and walks
+// the 128-row key/value blocks either tile attends to.  Per tile the score block S = Q K^T lives
+// in 128 fp32 columns of tensor memory, the probabilities P overwrite the front of those columns
+// in operand precision, and the output accumulator O holds another 128 columns:
+//     columns   0..127  S0 / P0      128..255  S1 / P1      256..383  O0      384..511  O1
+// Roles (12 warps, the last two idle so that every scheduler partition holds three):
+//     warps 0-3   softmax + O rescale + epilogue of tile 0 (one query row per thread)
+//     warps 4-7   the same for tile 1
+//     warp  8     MMA issue (one thread)
+//     warp  9     TMA loads (one thread)
+// The MMA thread interleaves the two tiles (S0, S1, PV0, S0', PV1, S1', ...) so the tensor pipe
+// has work of one tile while the other tile's rows are in the exponent unit.
+#include "fa_fwd.h"
+#include "ptx_sm100.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+namespace sdb {
+
+namespace {
+
+constexpr int kTile = 128;         // rows of a query tile and of a key/value block
+constexpr int kHeadDim = 128;
+constexpr int kThreads = 384;  // 12 warps: three per scheduler partition of the SM
+constexpr int kMmaWarp = 8;
+constexpr int kLoadWarp = 9;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units the running max may lag before O is rescaled
+constexpr float kFp8PShiftLog2 = 8.0f;     // e4m3 probabilities are stored as p * 2^8
+
+template <bool kFp8>
+struct Cfg {
+    static constexpr int kElemBytes = kFp8 ? 1 : 2;
+    static constexpr int kRowBytes = kHeadDim * kElemBytes;       // 256 / 128
+    static constexpr int kAtoms = kRowBytes / 128;                // 128-byte swizzle atoms per row
+    static constexpr int kAtomBytes = kTile * 128;                // 16 KB: 128 rows of one atom
+    static constexpr int kTileBytes = kAtoms * kAtomBytes;        // 32 KB / 16 KB
+    static constexpr int kStages = kFp8 ? 8 : 4;                  // ring slots, each one K or V block
+    static constexpr int kBoxInner = 128 / kElemBytes;            // elements of one 128-byte row
+    static constexpr int kQkSteps = kRowBytes / 32;               // MMAs per S block (32 B of K-dim each)
+    static constexpr int kPvK = 32 / kElemBytes;                  // kv rows per PV MMA (16 / 32)
+    static constexpr int kPvSteps = kTile / kPvK;                 // 8 / 4
+    static constexpr int kSmemBytes = 2 * kTileBytes + kStages * kTileBytes + 2 * kMaxKvBlocks + 256;
+};
+
+struct Ring {
+    int idx = 0;
+    uint32_t phase = 0;
+    template <int N>
+    __device__ __forceinline__ void next() {
+        if (++idx == N) {
+            idx = 0;
+            phase ^= 1u;
+        }
+    }
+};
+
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi, int dtype) {
+    if (dtype == 0) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ uint32_t pack_quad_e4m3(float a, float b, float c, float d) {
+    uint16_t lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+    return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+}  // namespace
+
+// kIn: element type of q/k/v and of the stored probabilities (0 bf16, 1 fp16, 3 e4m3).
+template <int kIn>
+__global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_constant__ FaParams p) {
+    constexpr bool kFp8 = kIn == 3;
+    using C = Cfg<kFp8>;
+    extern __shared__ uint8_t smem_raw[];
+    // The swizzle pattern of TMA and of the MMA descriptors is a function of the address bits, so
+    // operand tiles start on 1024-byte boundaries.
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sm_q = smem;                              // 2 tiles
+    uint8_t* sm_ring = smem + 2 * C::kTileBytes;       // kStages blocks
+    uint8_t* sm_flags = sm_ring + C::kStages * C::kTileBytes;  // [2][kMaxKvBlocks]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm_flags + 2 * kMaxKvBlocks);
+    // barrier map
+    const uint32_t bar_base = smem_u32(bars);
+    auto bar_q = [&]() { return bar_base; };
+    auto bar_full = [&](int s) { return bar_base + 8u * (1 + s); };
+    auto bar_empty = [&](int s) { return bar_base + 8u * (1 + C::kStages + s); };
+    auto bar_s = [&](int t) { return bar_base + 8u * (1 + 2 * C::kStages + t); };
+    auto bar_p = [&](int t) { return bar_base + 8u * (3 + 2 * C::kStages + t); };
+    constexpr int kNumBars = 5 + 2 * C::kStages;
+    static_assert(kNumBars * 8 + 16 <= 256, "barrier area");
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int qpair = blockIdx.x;
+    const int head = blockIdx.y;
+    const int batch = blockIdx.z;
+    const int kv_head = head / (p.heads / p.kv_heads);
+    const int q_row0 = qpair * 2 * kTile;
+    const bool tile1_valid = q_row0 + kTile < p.seq_q;
+    const int nkb = p.kv_blocks;
+
+    // ---- set-up -------------------------------------------------------------------------------
+    if (tid == 0) {
+        mbar_init(bar_q(), 1);
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(bar_s(t), 1);
+            mbar_init(bar_p(t), kTile);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == kLoadWarp && lane == 0) {
+        tma_prefetch_desc(&p.tm_q);
+        tma_prefetch_desc(&p.tm_k);
+        tma_prefetch_desc(&p.tm_v);
+    }
+    if (warp == 0) {
+        __syncwarp();
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    // Which kv blocks each tile attends to: one byte per (tile, block).
+    {
+        uint8_t* f0 = sm_flags;
+        uint8_t* f1 = sm_flags + kMaxKvBlocks;
+        const int qb0 = qpair * 2;
+        if (p.sparse_mode == 0) {
+            for (int j = tid; j < nkb; j += kThreads) {
+                f0[j] = 1;
+                f1[j] = tile1_valid ? 1 : 0;
+            }
+        } else if (p.sparse_mode == 1) {
+            const int8_t* m0 = p.block_mask + batch * p.mask_stride[0] + head * p.mask_stride[1] +
+                               static_cast<int64_t>(qb0) * p.mask_stride[2];
+            const int8_t* m1 = m0 + p.mask_stride[2];
+            for (int j = tid; j < nkb; j += kThreads) {
+                f0[j] = m0[j] != 0;
+                f1[j] = tile1_valid ? (m1[j] != 0) : 0;
+            }
+        } else {
+            for (int j = tid; j < nkb; j += kThreads) {
+                f0[j] = 0;
+                f1[j] = 0;
+            }
+            __syncthreads();
+            for (int t = 0; t < (tile1_valid ? 2 : 1); ++t) {
+                const int64_t row = static_cast<int64_t>(qb0 + t) * p.heads + head;
+                const int64_t* ids = p.select_idx + row * p.select_stride;
+                int64_t n = p.select_num[row];
+                if (n > nkb) n = nkb;
+                uint8_t* f = t ? f1 : f0;
+                for (int i = tid; i < n; i += kThreads) {
+                    const int64_t id = ids[i];
+                    if (id >= 0 && id < nkb) f[id] = 1;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint8_t* f0 = sm_flags;
+    const uint8_t* f1 = sm_flags + kMaxKvBlocks;
+    auto flags_of = [&](int j) -> int { return static_cast<int>(f0[j]) | (static_cast<int>(f1[j]) << 1); };
+    auto next_block = [&](int j) -> int {
+        while (j < nkb && flags_of(j) == 0) ++j;
+        return j < nkb ? j : -1;
+    };
+
+    if (warp == kLoadWarp) {
+        // ---- TMA producer ---------------------------------------------------------------------
+        if (lane == 0) {
+            const uint32_t q_bytes = (tile1_valid ? 2 : 1) * C::kTileBytes;
+            mbar_arrive_expect_tx(bar_q(), q_bytes);
+            for (int t = 0; t < (tile1_valid ? 2 : 1); ++t)
+                for (int a = 0; a < C::kAtoms; ++a)
+                    tma_load_4d(smem_u32(sm_q + t * C::kTileBytes + a * C::kAtomBytes), &p.tm_q, bar_q(),
+                                a * C::kBoxInner, q_row0 + t * kTile, head, batch);
+            Ring ring;
+            int issued = 0;
+            bool ok = true;
+            for (int u = next_block(0); u >= 0 && ok; u = next_block(u + 1)) {
+                for (int which = 0; which < 2 && ok; ++which) {  // 0: K block, 1: V block
+                    ok = mbar_wait(bar_empty(ring.idx), ring.phase ^ 1u, abort_flag);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(bar_full(ring.idx), C::kTileBytes);
+                    const CUtensorMap* tm = which ? &p.tm_v : &p.tm_k;
+                    for (int a = 0; a < C::kAtoms; ++a)
+                        tma_load_4d(smem_u32(sm_ring + ring.idx * C::kTileBytes + a * C::kAtomBytes), tm,
+                                    bar_full(ring.idx), a * C::kBoxInner, u * kTile, kv_head, batch);
+                    ring.template next<C::kStages>();
+                    ++issued;
+                }
+            }
+            // Before the CTA may exit, every copy this thread started must have landed.
+            mbar_wait(bar_q(), 0, abort_flag);
+            const int pending = issued < C::kStages ? issued : C::kStages;
+            for (int i = 0; i < pending; ++i) {
+                const int n = issued - 1 - i;  // n-th load overall
+                mbar_wait(bar_full(n % C::kStages), static_cast<uint32_t>(n / C::kStages) & 1u, abort_flag);
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ---- MMA issue ------------------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t fmt = kIn == 0 ? 1u : 0u;  // f16 kind: 1 = bf16, 0 = fp16; f8f6f4 kind: 0 = e4m3
+            const uint32_t idesc_qk = umma_idesc(fmt, kTile, kTile, false, false);
+            const uint32_t idesc_pv = umma_idesc(fmt, kTile, kHeadDim, false, true);
+            const uint32_t col_s[2] = {tmem_base + kColS0, tmem_base + kColS1};
+            const uint32_t col_o[2] = {tmem_base + kColO0, tmem_base + kColO1};
+
+            auto issue_s = [&](int t, int slot) {
+                const uint32_t qa = smem_u32(sm_q + t * C::kTileBytes);
+                const uint32_t ka = smem_u32(sm_ring + slot * C::kTileBytes);
+#pragma unroll
+                for (int kc = 0; kc < C::kQkSteps; ++kc) {
+                    const uint32_t off = (kc >> 2) * C::kAtomBytes + (kc & 3) * 32;
+                    umma_ss<kFp8>(col_s[t], smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024),
+                                  idesc_qk, kc > 0);
+                }
+                umma_commit(bar_s(t));
+            };
+            auto issue_pv = [&](int t, int slot, bool accumulate) {
+                const uint32_t va = smem_u32(sm_ring + slot * C::kTileBytes);
+#pragma unroll
+                for (int kc = 0; kc < C::kPvSteps; ++kc) {
+                    // A: 8 tensor-memory columns per step (16 two-byte or 32 one-byte probabilities).
+                    umma_ts<kFp8>(col_o[t], col_s[t] + kc * 8,
+                                  smem_desc_sw128(va + kc * C::kPvK * 128, C::kAtomBytes, 1024), idesc_pv,
+                                  (accumulate || kc > 0) ? 1u : 0u);
+                }
+            };
+
+            bool ok = mbar_wait(bar_q(), 0, abort_flag);
+            Ring ring;
+            int pv_cnt[2] = {0, 0};
+            int u = next_block(0);
+            if (ok && u >= 0) {
+                ok = mbar_wait(bar_full(ring.idx), ring.phase, abort_flag);
+                if (ok) {
+                    tc_fence_after();
+                    const int f = flags_of(u);
+                    if (f & 1) issue_s(0, ring.idx);
+                    if (f & 2) issue_s(1, ring.idx);
+                    umma_commit(bar_empty(ring.idx));
+                    ring.template next<C::kStages>();
+                }
+            }
+            while (ok && u >= 0) {
+                const int f = flags_of(u);
+                const int nu = next_block(u + 1);
+                const int nf = nu >= 0 ? flags_of(nu) : 0;
+                const Ring vslot = ring;
+                ring.template next<C::kStages>();
+                const Ring kslot = ring;
+                if (nf) ring.template next<C::kStages>();
+
+                ok = mbar_wait(bar_full(vslot.idx), vslot.phase, abort_flag);
+                if (!ok) break;
+                if (f & 1) {
+                    ok = mbar_wait(bar_p(0), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(0, vslot.idx, pv_cnt[0] > 0);
+                    ++pv_cnt[0];
+                }
+                if (nf) {
+                    ok = mbar_wait(bar_full(kslot.idx), kslot.phase, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                if (nf & 1) issue_s(0, kslot.idx);
+                if (f & 2) {
+                    ok = mbar_wait(bar_p(1), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(1, vslot.idx, pv_cnt[1] > 0);
+                    ++pv_cnt[1];
+                }
+                umma_commit(bar_empty(vslot.idx));
+                if (nf & 2) issue_s(1, kslot.idx);
+                if (nf) umma_commit(bar_empty(kslot.idx));
+                u = nu;
+            }
+            // Final arrival on each tile's S barrier: its output accumulator is complete.
+            umma_commit(bar_s(0));
+            umma_commit(bar_s(1));
+        }
+    } else if (warp < 8) {
+        // ---- softmax, O rescale, epilogue: one query row per thread ------------------------------
+        const int t = warp >> 2;  // tile of this warpgroup
+        const int row_in_tile = tid & (kTile - 1);
+        const int q_row = q_row0 + t * kTile + row_in_tile;
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t taddr_s = tmem_base + (t ? kColS1 : kColS0) + lane_base;
+        const uint32_t taddr_o = tmem_base + (t ? kColO1 : kColO0) + lane_base;
+        const uint8_t* my_flags = t ? f1 : f0;
+        const int tail_valid = p.seq_kv - (nkb - 1) * kTile;  // valid columns of the last kv block
+        // The running max may lag the true max by this much (log2 units) before O is rescaled; the
+        // probabilities then reach 2^lag, which two-byte formats hold but e4m3 does not.
+        constexpr float kLag = kFp8 ? 0.0f : kRescaleThreshold;
+
+        // e4m3: the dequantisation scales of the q block and of each k block fold into the
+        // exponent's multiplier; a per-token-block v scale folds into the exponent's offset.
+        float q_sc = 1.0f, v_ref = 1.0f;
+        const float* k_sc = nullptr;
+        const float* v_blk = nullptr;
+        if constexpr (kFp8) {
+            int qb = q_row0 / kTile + t;
+            if (qb >= p.q_blocks) qb = p.q_blocks - 1;
+            q_sc = p.q_scale[(static_cast<int64_t>(batch) * p.heads + head) * p.q_blocks + qb];
+            k_sc = p.k_scale + (static_cast<int64_t>(batch) * p.kv_heads + kv_head) * p.k_scale_count;
+            if (p.v_scale_block > 0) {
+                v_blk = p.v_scale + (static_cast<int64_t>(batch) * p.kv_heads + kv_head) * p.v_scale_count;
+                float mx = 0.0f;
+                for (int i = lane; i < p.v_scale_count; i += 32) mx = fmaxf(mx, v_blk[i]);
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+                v_ref = mx > 0.0f ? mx : 1.0f;
+            }
+        }
+
+        float m_run = -INFINITY;  // running row max, in log2 units of the scaled scores
+        float l_run = 0.0f;
+        int cnt = 0;
+        bool ok = true;
+        for (int j = 0; j < nkb; ++j) {
+            if (!my_flags[j]) continue;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_s(t), static_cast<uint32_t>(cnt) & 1u, abort_flag));
+            if (!ok) break;
+            tc_fence_after();
+
+            uint32_t s[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(taddr_s + c * 32, s[c]);
+            tmem_wait_ld();
+
+            float mult = p.scale_log2;
+            float v_off = 0.0f, l_fix = 1.0f;
+            if constexpr (kFp8) {
+                mult *= q_sc * k_sc[(j * kTile) / p.k_scale_block];
+                if (v_blk) {
+                    const float r = fmaxf(v_blk[(j * kTile) / p.v_scale_block], 1e-30f) / v_ref;
+                    v_off = log2f(r);
+                    l_fix = 1.0f / r;
+                }
+            }
+
+            if (j == nkb - 1 && tail_valid < kTile) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c * 32 + i >= tail_valid) s[c][i] = 0xff800000u;  // -inf
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+            const float m_cand = mx * mult;
+            const bool need = m_cand > m_run + kLag;
+            if (__any_sync(0xffffffffu, need)) {
+                const float m_new = fmaxf(m_run, m_cand);
+                const float alpha = ex2_approx(m_run - m_new);  // 0 on the first block (m_run = -inf)
+                if (cnt > 0) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(taddr_o + c * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(taddr_o + c * 32, o);
+                    }
+                }
+                l_run *= alpha;
+                m_run = m_new;
+            }
+            const float neg_m = kFp8 ? (kFp8PShiftLog2 + v_off - m_run) : -m_run;
+            float sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if constexpr (kFp8) {
+                    uint32_t pk[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float a = ex2_approx(fmaf(__uint_as_float(s[c][4 * i + 0]), mult, neg_m));
+                        const float b = ex2_approx(fmaf(__uint_as_float(s[c][4 * i + 1]), mult, neg_m));
+                        const float cc = ex2_approx(fmaf(__uint_as_float(s[c][4 * i + 2]), mult, neg_m));
+                        const float d = ex2_approx(fmaf(__uint_as_float(s[c][4 * i + 3]), mult, neg_m));
+                        sum += (a + b) + (cc + d);
+                        pk[i] = pack_quad_e4m3(a, b, cc, d);
+                    }
+                    tmem_st8(taddr_s + c * 8, pk);
+                } else {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float a = ex2_approx(fmaf(__uint_as_float(s[c][2 * i + 0]), mult, neg_m));
+                        const float b = ex2_approx(fmaf(__uint_as_float(s[c][2 * i + 1]), mult, neg_m));
+                        sum += a + b;
+                        pk[i] = pack_pair(a, b, kIn);
+                    }
+                    tmem_st16(taddr_s + c * 16, pk);
+                }
+            }
+            l_run += sum * l_fix;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar_p(t));
+            ++cnt;
+        }
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_s(t), static_cast<uint32_t>(cnt) & 1u, abort_flag));
+        if (ok && (t == 0 || tile1_valid)) {  // warp-uniform: the tensor-memory loads are warp-collective
+            tc_fence_after();
+            const bool row_ok = q_row < p.seq_q;
+            // l_run carries the 2^8 shift of the stored e4m3 probabilities, so it cancels in O / l.
+            const float inv_l = l_run > 0.0f ? v_ref / l_run : 0.0f;
+            const float* v_ch = (kFp8 && p.v_scale_block == 0)
+                                    ? p.v_scale + (static_cast<int64_t>(batch) * p.kv_heads + kv_head) * kHeadDim
+                                    : nullptr;
+            uint8_t* orow = static_cast<uint8_t*>(p.out) +
+                            (batch * p.o_stride[0] + head * p.o_stride[1] + static_cast<int64_t>(q_row) * p.o_stride[2]) *
+                                (p.out_dtype == 2 ? 4 : 2);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                if (cnt > 0) {
+                    tmem_ld32(taddr_o + c * 32, o);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = 0;
+                }
+                float vals[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float x = __uint_as_float(o[i]) * inv_l;
+                    if constexpr (kFp8)
+                        if (v_ch) x *= v_ch[c * 32 + i];
+                    vals[i] = x;
+                }
+                if (row_ok) {
+                    if (p.out_dtype == 2) {
+                        float4* dst = reinterpret_cast<float4*>(orow + c * 128);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            dst[i] = make_float4(vals[4 * i], vals[4 * i + 1], vals[4 * i + 2], vals[4 * i + 3]);
+                    } else {
+                        uint4* dst = reinterpret_cast<uint4*>(orow + c * 64);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint4 w;
+                            w.x = pack_pair(vals[8 * i + 0], vals[8 * i + 1], p.out_dtype);
+                            w.y = pack_pair(vals[8 * i + 2], vals[8 * i + 3], p.out_dtype);
+                            w.z = pack_pair(vals[8 * i + 4], vals[8 * i + 5], p.out_dtype);
+                            w.w = pack_pair(vals[8 * i + 6], vals[8 * i + 7], p.out_dtype);
+                            dst[i] = w;
+                        }
+                    }
+                }
+            }
+            if (p.lse && row_ok) {
+                const float shift = kFp8 ? kFp8PShiftLog2 : 0.0f;
+                p.lse[(static_cast<int64_t>(batch) * p.heads + head) * p.seq_q + q_row] =
+                    l_run > 0.0f ? (m_run - shift) * 0.6931471805599453f + logf(l_run) : -INFINITY;
+            }
+        }
+    }
+
+    // ---- teardown ---------------------------------------------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (tid == 0 && *abort_flag && p.status) atomicCAS(p.status, 0, kStatusFaWaitGaveUp);
+}
+
+int fa_fwd_smem_bytes(bool fp8) { return (fp8 ? Cfg<true>::kSmemBytes : Cfg<false>::kSmemBytes) + 1024; }
+
+template <int kIn>
+static cudaError_t launch_one(const FaParams& p, cudaStream_t stream) {
+    const int smem = fa_fwd_smem_bytes(kIn == 3);
+    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<kIn>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    dim3 grid((p.seq_q + 2 * kTile - 1) / (2 * kTile), p.heads, p.batch);
+    fa_fwd_kernel<kIn><<<grid, kThreads, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t fa_fwd_launch(const FaParams& p, cudaStream_t stream) {
+    switch (p.in_dtype) {
+        case 0: return launch_one<0>(p, stream);
+        case 1: return launch_one<1>(p, stream);
+        case 3: return launch_one<3>(p, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace sdb
