@@ -99,8 +99,9 @@ int mindiesd_attention_fwd(const mindiesd_attn_args* args, void* stream);
 /*
  * RainFusion token permutation of the image tokens of a (t, h, w) latent grid into 8x8 spatial
  * windows (forward) and back (inverse = 1), text tokens moved from the front to the back
- * (forward) or back to the front (inverse).  src/dst: [B, N, S, D] by element strides, 2-byte
- * elements, D a multiple of 8, S = txt_len + t*h*w.  dst must not alias src.
+ * (forward) or back to the front (inverse).  src/dst: [B, N, S, D] by element strides, elements
+ * of elem_bytes (1, 2 or 4) bytes, rows and strides multiples of 16 bytes, S = txt_len + t*h*w.
+ * dst must not alias src.
  *
  * Stands in for rearrange_with_remaining / inv_rearrange_with_remaining /
  * do_tensor_inv_rearrange (mindiesd/layers/flash_attn/sparse_flash_attn_rf_v2.py:137-196,
@@ -110,7 +111,7 @@ int mindiesd_attention_fwd(const mindiesd_attn_args* args, void* stream);
 typedef struct mindiesd_rearrange_args {
     const void* src;
     void* dst;
-    int32_t batch, heads, seq, head_dim;
+    int32_t batch, heads, seq, head_dim, elem_bytes;
     int64_t src_stride[3];
     int64_t dst_stride[3];
     int32_t t, h, w, txt_len;
@@ -144,8 +145,8 @@ typedef struct mindiesd_mask_args {
     int32_t dtype; /* MINDIESD_BF16 / FP16 / FP32 */
     int32_t t, h, w, txt_len;
     int32_t block_size; /* 128 */
-    float sparsity;
-    float scale;
+    float scale;        /* > 0; the kept set does not depend on its value */
+    double sparsity;    /* in [0, 1); double so that ceil(kv_blocks * (1 - sparsity)) equals the reference's */
     int32_t protect_first_frame;
     int32_t temporal_band; /* < 0: off (the reference has no band) */
     int8_t* mask;
@@ -159,11 +160,58 @@ size_t mindiesd_rf_block_mask_scratch_bytes(int32_t batch, int32_t heads, int32_
 int mindiesd_rf_block_mask(const mindiesd_mask_args* args, void* stream);
 
 /*
+ * The two stages of the mask builder on their own, for callers that use the reference's helper
+ * functions one at a time.
+ *
+ * mindiesd_rf_pool: fp32 means of 128-token blocks of x [B, N, S, D] -> pooled [B, N, blocks, D].
+ * permute = 0 pools consecutive tokens (blocks = ceil(S/128)); permute = 1 pools the
+ * window-permuted order of a (t, h, w) grid with txt_len leading text tokens, image and text
+ * separately (blocks = ceil(t*h*w/128) + ceil(txt_len/128)).
+ * Stands in for avgpool and the pooling half of do_tensor_rearrange_pooling
+ * (mindiesd/layers/flash_attn/sparse_flash_attn_rf_v2.py:24-73, 292-317).
+ *
+ * mindiesd_rf_mask_from_pooled: the mask / block lists from pooled q and k (fp32, contiguous
+ * [B, N, blocks, D]).  Stands in for get_blockwise_mask + get_mask_index (rf_v2.py:76-134).
+ */
+typedef struct mindiesd_pool_args {
+    const void* x;
+    float* pooled;
+    int32_t batch, heads, seq, head_dim;
+    int64_t x_stride[3];
+    int32_t dtype;
+    int32_t t, h, w, txt_len;
+    int32_t permute;
+    int32_t block_size; /* 128 */
+} mindiesd_pool_args;
+
+int mindiesd_rf_pool(const mindiesd_pool_args* args, void* stream);
+
+typedef struct mindiesd_pooled_mask_args {
+    const float* q_pooled;
+    const float* k_pooled;
+    int32_t batch, heads, blocks, head_dim;
+    int32_t t, h, w, txt_len;
+    int32_t block_size; /* 128 */
+    int32_t protect_first_frame;
+    int32_t temporal_band;
+    double sparsity;
+    int8_t* mask;
+    int64_t* select_idx;
+    int64_t* select_num;
+} mindiesd_pooled_mask_args;
+
+int mindiesd_rf_mask_from_pooled(const mindiesd_pooled_mask_args* args, void* stream);
+
+/*
  * Dynamic block quantisation to e4m3 for attention operands.  x: [B, N, S, D] bf16/fp16 by
  * element strides.  mode 0: one scale per (row_block tokens x 128 channels) block,
  * scale = absmax / 448 (1 where the block is all zero), scales fp32 [B, N, ceil(S/row_block)];
  * mode 1: one scale per channel over the whole sequence, scales fp32 [B, N, D].
  * out: e4m3 [B, N, S, D] contiguous.
+ * rotate: q and k rotated by the same orthogonal matrix give the same q k^T; the rotation spreads
+ * outlier channels so that the e4m3 rounding error of the scores stays small.  It fuses the
+ * reference's `query @ q_rot` / `key @ k_rot` (mindiesd/quantization/layer.py:284-285) into the
+ * quantisation pass for the fixed Hadamard rotation.
  *
  * Stands in for torch_npu.npu_dynamic_block_quant as called by fa_block_quant_preprocess
  * (mindiesd/layers/quant/block_quant.py:43-46).
@@ -177,6 +225,7 @@ typedef struct mindiesd_quant_args {
     int32_t dtype;
     int32_t mode;
     int32_t row_block; /* 128, 256 or 512 (mode 0) */
+    int32_t rotate;    /* mode 0: first rotate every token by the 128-point Walsh-Hadamard matrix / sqrt(128) */
 } mindiesd_quant_args;
 
 int mindiesd_fa_block_quant(const mindiesd_quant_args* args, void* stream);

@@ -90,12 +90,12 @@ def build_torch_ext(force: bool = False) -> Path:
         inc += ["-I", d]
     torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
     abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
-    cmd = [_nvcc()] + ARCH_FLAGS + ["-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared",
-                                    "-D_GLIBCXX_USE_CXX11_ABI=%d" % abi, "-DTORCH_EXTENSION_NAME=mindiesd_b200_ops",
-                                    "-I", str(INCLUDE)] + inc + \
-          [str(s) for s in srcs] + ["-o", str(TORCH_EXT_LIB), "-L", str(PLUGIN), "-lmindiesd_b200",
-                                    "-L", torch_lib, "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda", "-lc10_cuda",
-                                    "-Xlinker", "-rpath,$ORIGIN", "-Xlinker", "-rpath," + torch_lib]
+    cxx = shutil.which("g++") or "g++"
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-D_GLIBCXX_USE_CXX11_ABI=%d" % abi,
+           "-I", str(INCLUDE)] + inc + [str(s) for s in srcs] + \
+          ["-o", str(TORCH_EXT_LIB), "-L", str(PLUGIN), "-lmindiesd_b200",
+           "-L", torch_lib, "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda", "-lc10_cuda",
+           "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + torch_lib]
     _run(cmd)
     return TORCH_EXT_LIB
 

@@ -8,6 +8,8 @@
 
 namespace sdb {
 
+constexpr int kMaxMaskBlocks = 4096;  // 128-token blocks per sequence the mask builder accepts
+
 // Device address of the status word of the current device (NULL if the runtime refuses).
 int* device_status_word();
 
@@ -27,5 +29,8 @@ inline int dtype_bytes(int dtype) {
 // Returns MINDIESD_OK or a MINDIESD_E_* code.
 int encode_tile_map(CUtensorMap* map, const void* base, int dtype, int64_t channels, int64_t tokens,
                     int64_t heads, int64_t batch, const int64_t stride[3], int box_rows);
+
+// Pooling + mask kernels of the RainFusion mask builder with the pooled means in `pooled`.
+int rf_block_mask_impl(const mindiesd_mask_args* a, float* pooled, size_t pooled_bytes, cudaStream_t stream);
 
 }  // namespace sdb

@@ -1,0 +1,492 @@
+// RainFusion host-logic replacements, all HBM-bound byte/index work:
+//   * token permutation into 8x8 spatial windows and back (gather of 16-byte vectors),
+//   * pooled block means of the permuted q and k, read straight from the un-permuted tensors,
+//   * block scores, k-th-largest threshold per row and the int8 mask / compacted block lists.
+#include "capi_common.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace sdb {
+
+namespace {
+
+// Geometry of the window permutation of a (t, h, w) latent grid with txt_len text tokens.
+// Source order:   [text | image in (t, h, w) raster order]
+// Permuted order: [image, windows of 8x8 per frame | text]
+// When h or w is not a multiple of 8 the first frame stays in raster order and every later frame
+// is laid out as: full 8x8 windows, then the h-remainder rows (full width), then the w-remainder
+// columns of the windowed rows.
+struct Grid {
+    int t, h, w, txt;
+    int hw, img;        // tokens per frame, image tokens
+    int hm, wm, rh, rw; // windowed extent and remainders
+    int aligned;
+};
+
+__host__ __device__ inline Grid make_grid(int t, int h, int w, int txt) {
+    Grid g;
+    g.t = t; g.h = h; g.w = w; g.txt = txt;
+    g.hw = h * w;
+    g.img = t * h * w;
+    g.rh = h % 8; g.rw = w % 8;
+    g.hm = h - g.rh; g.wm = w - g.rw;
+    g.aligned = (g.rh == 0 && g.rw == 0);
+    return g;
+}
+
+// Source token (index into the source order) that lands at position p of the permuted order.
+__device__ __forceinline__ int source_of(const Grid& g, int p) {
+    if (p >= g.img) return p - g.img;  // text: back of the permuted order, front of the source
+    const int f = p / g.hw;
+    const int r = p - f * g.hw;
+    int y, x;
+    if (!g.aligned && f == 0) {
+        return g.txt + p;
+    }
+    const int win_area = g.hm * g.wm;
+    if (r < win_area) {
+        const int wpr = g.wm >> 3;  // windows per row of windows
+        const int win = r >> 6, in = r & 63;
+        const int wy = win / wpr, wx = win - wy * wpr;
+        y = wy * 8 + (in >> 3);
+        x = wx * 8 + (in & 7);
+    } else if (r < win_area + g.rh * g.w) {
+        const int r2 = r - win_area;
+        y = g.hm + r2 / g.w;
+        x = r2 % g.w;
+    } else {
+        const int r3 = r - win_area - g.rh * g.w;
+        y = r3 / g.rw;
+        x = g.wm + r3 % g.rw;
+    }
+    return g.txt + f * g.hw + y * g.w + x;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Permutation: one 16-byte vector per thread, consecutive threads along the channel dimension.
+// ------------------------------------------------------------------------------------------------
+struct RearrangeParams {
+    const uint4* src;
+    uint4* dst;
+    int64_t src_stride[3], dst_stride[3];  // in 16-byte vectors: batch, head, token
+    int heads, seq, vec_per_row;
+    Grid g;
+    int inverse;
+};
+
+__global__ void __launch_bounds__(256) rf_rearrange_kernel(const RearrangeParams p) {
+    const int rows_per_cta = 256 / p.vec_per_row;
+    const int v = threadIdx.x % p.vec_per_row;
+    const int r = threadIdx.x / p.vec_per_row;
+    const int head = blockIdx.y % p.heads;
+    const int batch = blockIdx.y / p.heads;
+    const int pos = blockIdx.x * rows_per_cta + r;  // position in the permuted order
+    if (r >= rows_per_cta || pos >= p.seq) return;
+    const int src_tok = source_of(p.g, pos);
+    const int from = p.inverse ? pos : src_tok;
+    const int to = p.inverse ? src_tok : pos;
+    const uint4 val = p.src[batch * p.src_stride[0] + head * p.src_stride[1] + from * p.src_stride[2] + v];
+    p.dst[batch * p.dst_stride[0] + head * p.dst_stride[1] + to * p.dst_stride[2] + v] = val;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Pooled means.  Grid: (block, head, batch * ntensors) -- with two tensors the low bit of the last
+// index selects q or k.
+// A block is up to 128 consecutive positions of the permuted image, or of the text; image and
+// text are pooled separately, so the last image block and the last text block may be short.
+// Sums are exact in fp64 (the operands are 8- or 11-bit-mantissa values); the mean is rounded
+// once to fp32.
+// ------------------------------------------------------------------------------------------------
+struct PoolParams {
+    const void* x[2];
+    int64_t stride[2][3];  // elements
+    float* pooled[2];      // each [batch][heads][blocks][dim]
+    int heads, dim, dtype;
+    int img_blocks, blocks;
+    Grid g;
+};
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* ptr, float (&out)[8]);
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* ptr, float (&out)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(ptr);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out[2 * i] = __uint_as_float(w[i] << 16);
+        out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+template <>
+__device__ __forceinline__ void load8<__half>(const __half* ptr, float (&out)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(ptr);
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        out[2 * i] = f.x;
+        out[2 * i + 1] = f.y;
+    }
+}
+template <>
+__device__ __forceinline__ void load8<float>(const float* ptr, float (&out)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(ptr);
+    const float4 b = *reinterpret_cast<const float4*>(ptr + 4);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+    out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) rf_pool_kernel(const PoolParams p, int ntensors) {
+    extern __shared__ double red[];  // [row groups][dim]
+    const int blk = blockIdx.x, head = blockIdx.y;
+    const int which = ntensors == 2 ? (blockIdx.z & 1) : 0;
+    const int batch = ntensors == 2 ? (blockIdx.z >> 1) : blockIdx.z;
+    const int lanes = p.dim >> 3;           // threads per token row
+    const int groups = 256 / lanes;         // token rows in flight
+    const int c = threadIdx.x % lanes, grp = threadIdx.x / lanes;
+
+    int first, count;
+    if (blk < p.img_blocks) {
+        first = blk * 128;
+        count = min(128, p.g.img - first);
+    } else {
+        first = p.g.img + (blk - p.img_blocks) * 128;
+        count = min(128, p.g.img + p.g.txt - first);
+    }
+    const T* base = static_cast<const T*>(p.x[which]) + batch * p.stride[which][0] + head * p.stride[which][1];
+    double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (grp < groups) {
+        for (int r = grp; r < count; r += groups) {
+            const int tok = source_of(p.g, first + r);
+            float vals[8];
+            load8<T>(base + tok * p.stride[which][2] + c * 8, vals);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += static_cast<double>(vals[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) red[grp * p.dim + c * 8 + i] = acc[i];
+    }
+    __syncthreads();
+    for (int ch = threadIdx.x; ch < p.dim; ch += 256) {
+        double s = 0;
+        for (int g2 = 0; g2 < groups; ++g2) s += red[g2 * p.dim + ch];
+        const int64_t o = ((static_cast<int64_t>(batch) * p.heads + head) * p.blocks + blk) * p.dim + ch;
+        p.pooled[which][o] = static_cast<float>(s / static_cast<double>(count));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Scores, threshold, mask.  One CTA per (group of `rows` q-blocks, head, batch); 256 threads.
+// Scores are fp64 dot products of the fp32 pooled means; the softmax of the reference is a
+// monotone map of each row, so the k-th largest is selected on the raw scores.
+// ------------------------------------------------------------------------------------------------
+struct MaskParams {
+    const float* q_pooled;  // [batch][heads][blocks][dim]
+    const float* k_pooled;
+    int heads, dim, blocks, rows;
+    int keep_len;
+    int txt_blocks, first_frame_blocks;
+    int band;  // < 0: off
+    Grid g;
+    int img_blocks;
+    int8_t* mask;         // [batch][heads][blocks][blocks]
+    int64_t* select_idx;  // [blocks][heads][blocks], batch 0
+    int64_t* select_num;  // [blocks][heads]
+};
+
+__device__ __forceinline__ unsigned long long order_key(double v) {
+    const unsigned long long b = static_cast<unsigned long long>(__double_as_longlong(v));
+    return (b >> 63) ? ~b : (b | 0x8000000000000000ull);
+}
+
+__global__ void __launch_bounds__(256) rf_mask_kernel(const MaskParams p) {
+    extern __shared__ unsigned char smem_dyn[];
+    // layout: q rows [rows][dim] float | k tile [32][dim + 1] float | keys [rows][blocks] u64
+    float* sq = reinterpret_cast<float*>(smem_dyn);
+    float* sk = sq + p.rows * p.dim;
+    const int kpitch = p.dim + 1;
+    unsigned long long* keys =
+        reinterpret_cast<unsigned long long*>(smem_dyn + ((static_cast<size_t>(p.rows) * p.dim + 32 * kpitch) * 4 + 7) / 8 * 8);
+
+    const int row0 = blockIdx.x * p.rows, head = blockIdx.y, batch = blockIdx.z;
+    const int nrows = min(p.rows, p.blocks - row0);
+    const int tid = threadIdx.x;
+    const float* qp = p.q_pooled + ((static_cast<int64_t>(batch) * p.heads + head) * p.blocks) * p.dim;
+    const float* kp = p.k_pooled + ((static_cast<int64_t>(batch) * p.heads + head) * p.blocks) * p.dim;
+
+    for (int i = tid; i < nrows * p.dim; i += 256) sq[i] = qp[static_cast<int64_t>(row0) * p.dim + i];
+
+    // Scores, 32 k-blocks at a time: thread (r, j) = (tid / 32, tid % 32) for rows r, r + 8, ...
+    for (int j0 = 0; j0 < p.blocks; j0 += 32) {
+        __syncthreads();
+        const int nj = min(32, p.blocks - j0);
+        for (int i = tid; i < nj * p.dim; i += 256) {
+            const int j = i / p.dim, ch = i - j * p.dim;
+            sk[j * kpitch + ch] = kp[static_cast<int64_t>(j0 + j) * p.dim + ch];
+        }
+        __syncthreads();
+        const int j = tid & 31;
+        if (j < nj) {
+            for (int r = tid >> 5; r < nrows; r += 8) {
+                double acc = 0.0;
+                const float* a = sq + r * p.dim;
+                const float* b = sk + j * kpitch;
+                for (int ch = 0; ch < p.dim; ++ch) acc = fma(static_cast<double>(a[ch]), static_cast<double>(b[ch]), acc);
+                keys[static_cast<size_t>(r) * p.blocks + j0 + j] = order_key(acc);
+            }
+        }
+    }
+    __syncthreads();
+
+    // One warp per row: bitwise search for the largest key value that at least keep_len keys reach.
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int r = warp; r < nrows; r += 8) {
+        const unsigned long long* kr = keys + static_cast<size_t>(r) * p.blocks;
+        unsigned long long thr = 0;
+        for (int bit = 63; bit >= 0; --bit) {
+            const unsigned long long cand = thr | (1ull << bit);
+            int cnt = 0;
+            for (int j = lane; j < p.blocks; j += 32) cnt += kr[j] >= cand;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, d);
+            if (cnt >= p.keep_len) thr = cand;
+        }
+        const int qb = row0 + r;
+        const bool row_forced = qb >= p.blocks - p.txt_blocks || qb < p.first_frame_blocks;
+        // Frame range of the q block (image blocks only), for the optional temporal band.
+        int q_lo = 0, q_hi = 0;
+        const bool q_img = qb < p.img_blocks;
+        if (p.band >= 0 && q_img) {
+            q_lo = (qb * 128) / p.g.hw;
+            q_hi = (min(qb * 128 + 128, p.g.img) - 1) / p.g.hw;
+        }
+        int8_t* mrow = p.mask ? p.mask + ((static_cast<int64_t>(batch) * p.heads + head) * p.blocks + qb) * p.blocks : nullptr;
+        int64_t* lrow = (p.select_idx && batch == 0)
+                            ? p.select_idx + (static_cast<int64_t>(qb) * p.heads + head) * p.blocks
+                            : nullptr;
+        int kept = 0;
+        for (int j0 = 0; j0 < p.blocks; j0 += 32) {
+            const int j = j0 + lane;
+            bool keep = false;
+            if (j < p.blocks) {
+                keep = row_forced || kr[j] >= thr || j >= p.blocks - p.txt_blocks || j < p.first_frame_blocks;
+                if (!keep && p.band >= 0 && q_img && j < p.img_blocks) {
+                    const int k_lo = (j * 128) / p.g.hw;
+                    const int k_hi = (min(j * 128 + 128, p.g.img) - 1) / p.g.hw;
+                    keep = (k_lo - p.band <= q_hi) && (q_lo - p.band <= k_hi);
+                }
+                if (mrow) mrow[j] = keep ? 1 : 0;
+            }
+            const unsigned ballot = __ballot_sync(0xffffffffu, keep);
+            if (lrow && keep) lrow[kept + __popc(ballot & ((1u << lane) - 1u))] = j;
+            kept += __popc(ballot);
+        }
+        if (lrow) {
+            for (int j = kept + lane; j < p.blocks; j += 32) lrow[j] = -1;
+            if (lane == 0 && p.select_num) p.select_num[static_cast<int64_t>(qb) * p.heads + head] = kept;
+        }
+    }
+}
+
+int mask_rows_per_cta(int blocks) { return blocks <= 1024 ? 8 : (blocks <= 2048 ? 4 : 2); }
+
+size_t mask_smem_bytes(int rows, int dim, int blocks) {
+    return ((static_cast<size_t>(rows) * dim + 32 * (dim + 1)) * 4 + 7) / 8 * 8 + static_cast<size_t>(rows) * blocks * 8;
+}
+
+}  // namespace
+
+}  // namespace sdb
+
+using namespace sdb;
+
+extern "C" int mindiesd_rf_rearrange(const mindiesd_rearrange_args* a, void* stream) {
+    if (!a || !a->src || !a->dst) return MINDIESD_E_NULL;
+    if (a->src == a->dst) return MINDIESD_E_VALUE;
+    if (a->batch <= 0 || a->heads <= 0 || a->seq <= 0 || a->head_dim <= 0) return MINDIESD_E_SHAPE;
+    const int eb = a->elem_bytes;
+    if (eb != 1 && eb != 2 && eb != 4) return MINDIESD_E_DTYPE;
+    const int vec = 16 / eb;  // elements per 16-byte vector
+    if (a->head_dim % vec || a->head_dim / vec > 256) return MINDIESD_E_SHAPE;
+    if (a->t <= 0 || a->h <= 0 || a->w <= 0 || a->txt_len < 0) return MINDIESD_E_SHAPE;
+    if (static_cast<int64_t>(a->t) * a->h * a->w + a->txt_len != a->seq) return MINDIESD_E_SHAPE;
+    // The reference's permutation is undefined for a ragged grid with fewer than 8 rows or columns.
+    if ((a->h % 8 || a->w % 8) && (a->h < 8 || a->w < 8)) return MINDIESD_E_SHAPE;
+    if (static_cast<int64_t>(a->batch) * a->heads > 65535) return MINDIESD_E_SHAPE;
+    if (reinterpret_cast<uintptr_t>(a->src) % 16 || reinterpret_cast<uintptr_t>(a->dst) % 16) return MINDIESD_E_STRIDE;
+    RearrangeParams p;
+    p.src = static_cast<const uint4*>(a->src);
+    p.dst = static_cast<uint4*>(a->dst);
+    for (int i = 0; i < 3; ++i) {
+        if (a->src_stride[i] % vec || a->dst_stride[i] % vec) return MINDIESD_E_STRIDE;
+        p.src_stride[i] = a->src_stride[i] / vec;
+        p.dst_stride[i] = a->dst_stride[i] / vec;
+    }
+    p.heads = a->heads;
+    p.seq = a->seq;
+    p.vec_per_row = a->head_dim / vec;
+    p.g = make_grid(a->t, a->h, a->w, a->txt_len);
+    p.inverse = a->inverse ? 1 : 0;
+    const int rows_per_cta = 256 / p.vec_per_row;
+    dim3 grid((a->seq + rows_per_cta - 1) / rows_per_cta, a->batch * a->heads);
+    rf_rearrange_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? MINDIESD_OK : static_cast<int>(e);
+}
+
+extern "C" size_t mindiesd_rf_block_mask_scratch_bytes(int32_t batch, int32_t heads, int32_t seq, int32_t head_dim) {
+    if (batch <= 0 || heads <= 0 || seq <= 0 || head_dim <= 0) return 0;
+    // Image and text are pooled separately, so there is at most one block more than ceil(seq / 128).
+    const size_t blocks = static_cast<size_t>(seq + 127) / 128 + 1;
+    return static_cast<size_t>(batch) * 2 * heads * blocks * head_dim * sizeof(float);
+}
+
+namespace sdb {
+
+namespace {
+
+bool grid_ok(int t, int h, int w, int txt_len, int64_t seq) {
+    if (t < 0 || h < 0 || w < 0 || txt_len < 0) return false;
+    if (static_cast<int64_t>(t) * h * w + txt_len != seq) return false;
+    // The reference's permutation is undefined for a ragged grid with fewer than 8 rows or columns.
+    if (static_cast<int64_t>(t) * h * w > 0 && (h % 8 || w % 8) && (h < 8 || w < 8)) return false;
+    return true;
+}
+
+int launch_pool(const void* const x[2], const int64_t* const stride[2], float* const pooled[2], int ntensors, int batch,
+                int heads, int seq, int dim, int dtype, const Grid& g, cudaStream_t stream) {
+    if (dim <= 0 || dim % 8 || dim > 256 || 256 % (dim / 8)) return MINDIESD_E_SHAPE;
+    if (dtype != MINDIESD_BF16 && dtype != MINDIESD_FP16 && dtype != MINDIESD_FP32) return MINDIESD_E_DTYPE;
+    if (batch <= 0 || heads <= 0 || seq <= 0 || batch > 32767 || heads > 65535) return MINDIESD_E_SHAPE;
+    const int vec = 16 / dtype_bytes(dtype);
+    PoolParams pp;
+    for (int w = 0; w < 2; ++w) {
+        const int src = w < ntensors ? w : 0;
+        if (!x[src] || !pooled[src]) return MINDIESD_E_NULL;
+        if (reinterpret_cast<uintptr_t>(x[src]) % 16 || reinterpret_cast<uintptr_t>(pooled[src]) % 4) return MINDIESD_E_STRIDE;
+        pp.x[w] = x[src];
+        pp.pooled[w] = pooled[src];
+        for (int i = 0; i < 3; ++i) {
+            if (stride[src][i] % vec) return MINDIESD_E_STRIDE;
+            pp.stride[w][i] = stride[src][i];
+        }
+    }
+    pp.heads = heads;
+    pp.dim = dim;
+    pp.dtype = dtype;
+    pp.img_blocks = (g.img + 127) / 128;
+    pp.blocks = pp.img_blocks + (g.txt + 127) / 128;
+    pp.g = g;
+    dim3 grid(pp.blocks, heads, batch * ntensors);
+    const size_t smem = static_cast<size_t>(256 / (dim / 8)) * dim * sizeof(double);
+    if (dtype == MINDIESD_BF16)
+        rf_pool_kernel<__nv_bfloat16><<<grid, 256, smem, stream>>>(pp, ntensors);
+    else if (dtype == MINDIESD_FP16)
+        rf_pool_kernel<__half><<<grid, 256, smem, stream>>>(pp, ntensors);
+    else
+        rf_pool_kernel<float><<<grid, 256, smem, stream>>>(pp, ntensors);
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? MINDIESD_OK : static_cast<int>(e);
+}
+
+int launch_mask(const float* q_pooled, const float* k_pooled, int batch, int heads, int dim, const Grid& g,
+                double sparsity, int protect_first_frame, int band, int8_t* mask, int64_t* select_idx,
+                int64_t* select_num, cudaStream_t stream) {
+    if (!q_pooled || !k_pooled) return MINDIESD_E_NULL;
+    if (!mask && !select_idx) return MINDIESD_E_NULL;
+    if (select_idx && !select_num) return MINDIESD_E_NULL;
+    if (batch <= 0 || heads <= 0 || dim <= 0 || batch > 65535 || heads > 65535) return MINDIESD_E_SHAPE;
+    if (!(sparsity >= 0.0) || !(sparsity < 1.0)) return MINDIESD_E_VALUE;
+    MaskParams mp;
+    mp.q_pooled = q_pooled;
+    mp.k_pooled = k_pooled;
+    mp.heads = heads;
+    mp.dim = dim;
+    mp.img_blocks = (g.img + 127) / 128;
+    mp.txt_blocks = (g.txt + 127) / 128;
+    mp.blocks = mp.img_blocks + mp.txt_blocks;
+    if (mp.blocks < 1) return MINDIESD_E_SHAPE;
+    if (mp.blocks > kMaxMaskBlocks) return MINDIESD_E_CAPACITY;
+    mp.rows = mask_rows_per_cta(mp.blocks);
+    // Same double-precision expression as the reference's math.ceil(cols * (1 - sparsity)).
+    mp.keep_len = static_cast<int>(ceil(static_cast<double>(mp.blocks) * (1.0 - sparsity)));
+    if (mp.keep_len < 1) return MINDIESD_E_VALUE;
+    if (mp.keep_len > mp.blocks) mp.keep_len = mp.blocks;
+    mp.first_frame_blocks = protect_first_frame ? (g.hw + 127) / 128 : 0;
+    if (mp.first_frame_blocks > mp.blocks) mp.first_frame_blocks = mp.blocks;
+    mp.band = band;
+    mp.g = g;
+    mp.mask = mask;
+    mp.select_idx = select_idx;
+    mp.select_num = select_num;
+    const size_t smem = mask_smem_bytes(mp.rows, mp.dim, mp.blocks);
+    cudaError_t e = cudaFuncSetAttribute(rf_mask_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    dim3 grid((mp.blocks + mp.rows - 1) / mp.rows, heads, batch);
+    rf_mask_kernel<<<grid, 256, smem, stream>>>(mp);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? MINDIESD_OK : static_cast<int>(e);
+}
+
+}  // namespace
+
+int rf_block_mask_impl(const mindiesd_mask_args* a, float* pooled, size_t pooled_bytes, cudaStream_t stream) {
+    if (!a || !a->q || !a->k || !pooled) return MINDIESD_E_NULL;
+    if (a->block_size != 128) return MINDIESD_E_SHAPE;
+    if (a->batch <= 0 || a->heads <= 0 || a->seq <= 0 || a->head_dim <= 0) return MINDIESD_E_SHAPE;
+    if (a->t <= 0 || a->h <= 0 || a->w <= 0) return MINDIESD_E_SHAPE;
+    if (!grid_ok(a->t, a->h, a->w, a->txt_len, a->seq)) return MINDIESD_E_SHAPE;
+    if (!(a->scale > 0.0f)) return MINDIESD_E_VALUE;
+    const Grid g = make_grid(a->t, a->h, a->w, a->txt_len);
+    const int blocks = (g.img + 127) / 128 + (a->txt_len + 127) / 128;
+    const size_t per_tensor = static_cast<size_t>(a->batch) * a->heads * blocks * a->head_dim;
+    if (pooled_bytes < 2 * per_tensor * sizeof(float)) return MINDIESD_E_CAPACITY;
+    if (reinterpret_cast<uintptr_t>(pooled) % 16) return MINDIESD_E_STRIDE;
+    const void* x[2] = {a->q, a->k};
+    const int64_t* strides[2] = {a->q_stride, a->k_stride};
+    float* out[2] = {pooled, pooled + per_tensor};
+    int rc = launch_pool(x, strides, out, 2, a->batch, a->heads, a->seq, a->head_dim, a->dtype, g, stream);
+    if (rc) return rc;
+    return launch_mask(out[0], out[1], a->batch, a->heads, a->head_dim, g, a->sparsity, a->protect_first_frame,
+                       a->temporal_band, a->mask, a->select_idx, a->select_num, stream);
+}
+}  // namespace sdb
+
+extern "C" int mindiesd_rf_block_mask(const mindiesd_mask_args* a, void* stream) {
+    if (!a) return MINDIESD_E_NULL;
+    return rf_block_mask_impl(a, static_cast<float*>(a->scratch), a->scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mindiesd_rf_pool(const mindiesd_pool_args* a, void* stream) {
+    if (!a || !a->x || !a->pooled) return MINDIESD_E_NULL;
+    if (a->block_size != 128) return MINDIESD_E_SHAPE;
+    Grid g;
+    if (a->permute) {
+        if (a->t <= 0 || a->h <= 0 || a->w <= 0) return MINDIESD_E_SHAPE;
+        if (!grid_ok(a->t, a->h, a->w, a->txt_len, a->seq)) return MINDIESD_E_SHAPE;
+        g = make_grid(a->t, a->h, a->w, a->txt_len);
+    } else {
+        g = make_grid(0, 1, 1, a->seq);  // no image part: consecutive tokens are pooled as they lie
+    }
+    const void* x[2] = {a->x, a->x};
+    const int64_t* strides[2] = {a->x_stride, a->x_stride};
+    float* out[2] = {a->pooled, a->pooled};
+    return launch_pool(x, strides, out, 1, a->batch, a->heads, a->seq, a->head_dim, a->dtype, g,
+                       static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mindiesd_rf_mask_from_pooled(const mindiesd_pooled_mask_args* a, void* stream) {
+    if (!a) return MINDIESD_E_NULL;
+    if (a->block_size != 128) return MINDIESD_E_SHAPE;
+    if (a->t <= 0 || a->h <= 0 || a->w <= 0 || a->txt_len < 0) return MINDIESD_E_SHAPE;
+    const Grid g = make_grid(a->t, a->h, a->w, a->txt_len);
+    const int blocks = (g.img + 127) / 128 + (a->txt_len + 127) / 128;
+    if (blocks != a->blocks) return MINDIESD_E_SHAPE;
+    if (a->head_dim > 1024) return MINDIESD_E_SHAPE;
+    return launch_mask(a->q_pooled, a->k_pooled, a->batch, a->heads, a->head_dim, g, a->sparsity,
+                       a->protect_first_frame, a->temporal_band, a->mask, a->select_idx, a->select_num,
+                       static_cast<cudaStream_t>(stream));
+}

@@ -52,6 +52,7 @@ class RearrangeArgs(C.Structure):
     _fields_ = [
         ("src", C.c_void_p), ("dst", C.c_void_p),
         ("batch", C.c_int32), ("heads", C.c_int32), ("seq", C.c_int32), ("head_dim", C.c_int32),
+        ("elem_bytes", C.c_int32),
         ("src_stride", C.c_int64 * 3), ("dst_stride", C.c_int64 * 3),
         ("t", C.c_int32), ("h", C.c_int32), ("w", C.c_int32), ("txt_len", C.c_int32),
         ("inverse", C.c_int32),
@@ -65,10 +66,32 @@ class MaskArgs(C.Structure):
         ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3),
         ("dtype", C.c_int32),
         ("t", C.c_int32), ("h", C.c_int32), ("w", C.c_int32), ("txt_len", C.c_int32),
-        ("block_size", C.c_int32), ("sparsity", C.c_float), ("scale", C.c_float),
+        ("block_size", C.c_int32), ("scale", C.c_float), ("sparsity", C.c_double),
         ("protect_first_frame", C.c_int32), ("temporal_band", C.c_int32),
         ("mask", C.c_void_p), ("select_idx", C.c_void_p), ("select_num", C.c_void_p),
         ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t),
+    ]
+
+
+class PoolArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("pooled", C.c_void_p),
+        ("batch", C.c_int32), ("heads", C.c_int32), ("seq", C.c_int32), ("head_dim", C.c_int32),
+        ("x_stride", C.c_int64 * 3),
+        ("dtype", C.c_int32),
+        ("t", C.c_int32), ("h", C.c_int32), ("w", C.c_int32), ("txt_len", C.c_int32),
+        ("permute", C.c_int32), ("block_size", C.c_int32),
+    ]
+
+
+class PooledMaskArgs(C.Structure):
+    _fields_ = [
+        ("q_pooled", C.c_void_p), ("k_pooled", C.c_void_p),
+        ("batch", C.c_int32), ("heads", C.c_int32), ("blocks", C.c_int32), ("head_dim", C.c_int32),
+        ("t", C.c_int32), ("h", C.c_int32), ("w", C.c_int32), ("txt_len", C.c_int32),
+        ("block_size", C.c_int32), ("protect_first_frame", C.c_int32), ("temporal_band", C.c_int32),
+        ("sparsity", C.c_double),
+        ("mask", C.c_void_p), ("select_idx", C.c_void_p), ("select_num", C.c_void_p),
     ]
 
 
@@ -77,7 +100,7 @@ class QuantArgs(C.Structure):
         ("x", C.c_void_p), ("out", C.c_void_p), ("scales", C.c_void_p),
         ("batch", C.c_int32), ("heads", C.c_int32), ("seq", C.c_int32), ("head_dim", C.c_int32),
         ("x_stride", C.c_int64 * 3),
-        ("dtype", C.c_int32), ("mode", C.c_int32), ("row_block", C.c_int32),
+        ("dtype", C.c_int32), ("mode", C.c_int32), ("row_block", C.c_int32), ("rotate", C.c_int32),
     ]
 
 
@@ -103,7 +126,7 @@ def lib():
             raise NativeLibraryError(f"cannot load {path}: {exc}") from exc
         handle.mindiesd_abi_version.restype = C.c_int
         for name in ("mindiesd_attention_fwd", "mindiesd_rf_rearrange", "mindiesd_rf_block_mask",
-                     "mindiesd_fa_block_quant"):
+                     "mindiesd_rf_pool", "mindiesd_rf_mask_from_pooled", "mindiesd_fa_block_quant"):
             fn = getattr(handle, name, None)
             if fn is not None:
                 fn.restype = C.c_int
@@ -151,3 +174,122 @@ def strides_bns(x: torch.Tensor, head_first: bool):
         raise NativeLibraryError("the channel dimension must be contiguous")
     sb, s1, s2, _ = x.stride()
     return (sb, s1, s2) if head_first else (sb, s2, s1)
+
+
+# ---- convenience callers: torch tensors in, torch tensors out, nothing else between ---------------
+
+def _dims(x, head_first):
+    b, d = x.shape[0], x.shape[3]
+    n, s = (x.shape[1], x.shape[2]) if head_first else (x.shape[2], x.shape[1])
+    return b, n, s, d
+
+
+def attention(q, k, v, head_first=True, scale=None, block_mask=None, select_idx=None, select_num=None,
+              out_dtype=None, want_lse=False, q_scale=None, k_scale=None, v_scale=None, k_scale_block=0,
+              v_scale_block=0, out=None):
+    """mindiesd_attention_fwd on the current stream.  Returns out, or (out, lse) when want_lse."""
+    b, n, sq, d = _dims(q, head_first)
+    _, nkv, skv, _ = _dims(k, head_first)
+    if out is None:
+        odt = out_dtype or (q.dtype if q.dtype != torch.float8_e4m3fn else torch.bfloat16)
+        out = torch.empty(q.shape, dtype=odt, device=q.device)
+    a = AttnArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    lse = None
+    if want_lse:
+        lse = torch.empty(b, n, sq, dtype=torch.float32, device=q.device)
+        a.lse = lse.data_ptr()
+    a.batch, a.heads, a.kv_heads, a.seq_q, a.seq_kv, a.head_dim = b, n, nkv, sq, skv, d
+    a.q_stride[:] = strides_bns(q, head_first)
+    a.k_stride[:] = strides_bns(k, head_first)
+    a.v_stride[:] = strides_bns(v, head_first)
+    a.o_stride[:] = strides_bns(out, head_first)
+    a.in_dtype, a.out_dtype = dtype_code(q.dtype), dtype_code(out.dtype)
+    a.scale = float(scale if scale is not None else d ** -0.5)
+    a.block_size = 128
+    if block_mask is not None:
+        a.sparse_mode = SPARSE_MASK
+        a.block_mask = block_mask.data_ptr()
+        a.mask_stride[:] = (block_mask.stride(0), block_mask.stride(1), block_mask.stride(2))
+    elif select_idx is not None:
+        a.sparse_mode = SPARSE_LIST
+        a.select_idx, a.select_num = select_idx.data_ptr(), select_num.data_ptr()
+    if q_scale is not None:
+        a.q_scale, a.k_scale, a.v_scale = q_scale.data_ptr(), k_scale.data_ptr(), v_scale.data_ptr()
+        a.k_scale_block, a.v_scale_block = k_scale_block, v_scale_block
+    check(lib().mindiesd_attention_fwd(C.byref(a), current_stream_ptr(q.device)), "mindiesd_attention_fwd")
+    return (out, lse) if want_lse else out
+
+
+def rf_rearrange(x, grid, txt_len=0, head_first=True, inverse=False):
+    b, n, s, d = _dims(x, head_first)
+    dst = torch.empty_like(x)
+    a = RearrangeArgs()
+    a.src, a.dst = x.data_ptr(), dst.data_ptr()
+    a.batch, a.heads, a.seq, a.head_dim, a.elem_bytes = b, n, s, d, x.element_size()
+    a.src_stride[:] = strides_bns(x, head_first)
+    a.dst_stride[:] = strides_bns(dst, head_first)
+    a.t, a.h, a.w = grid
+    a.txt_len, a.inverse = txt_len, int(inverse)
+    check(lib().mindiesd_rf_rearrange(C.byref(a), current_stream_ptr(x.device)), "mindiesd_rf_rearrange")
+    return dst
+
+
+def rf_block_mask(q, k, grid, txt_len=0, sparsity=0.0, head_first=True, protect_first_frame=True, temporal_band=-1,
+                  want_lists=False, scratch=None):
+    b, n, s, d = _dims(q, head_first)
+    blocks = (grid[0] * grid[1] * grid[2] + 127) // 128 + (txt_len + 127) // 128
+    mask = torch.empty(b, n, blocks, blocks, dtype=torch.int8, device=q.device)
+    a = MaskArgs()
+    a.q, a.k = q.data_ptr(), k.data_ptr()
+    a.batch, a.heads, a.seq, a.head_dim = b, n, s, d
+    a.q_stride[:] = strides_bns(q, head_first)
+    a.k_stride[:] = strides_bns(k, head_first)
+    a.dtype = dtype_code(q.dtype)
+    a.t, a.h, a.w = grid
+    a.txt_len, a.block_size, a.scale, a.sparsity = txt_len, 128, d ** -0.5, float(sparsity)
+    a.protect_first_frame, a.temporal_band = int(protect_first_frame), temporal_band
+    a.mask = mask.data_ptr()
+    sel = num = None
+    if want_lists:
+        sel = torch.empty(blocks, n, blocks, dtype=torch.int64, device=q.device)
+        num = torch.empty(blocks, n, dtype=torch.int64, device=q.device)
+        a.select_idx, a.select_num = sel.data_ptr(), num.data_ptr()
+    nbytes = lib().mindiesd_rf_block_mask_scratch_bytes(b, n, s, d)
+    if scratch is None:
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    a.scratch, a.scratch_bytes = scratch.data_ptr(), scratch.numel()
+    check(lib().mindiesd_rf_block_mask(C.byref(a), current_stream_ptr(q.device)), "mindiesd_rf_block_mask")
+    return (mask, sel, num) if want_lists else mask
+
+
+def rf_pool(x, grid=None, txt_len=0, head_first=True):
+    b, n, s, d = _dims(x, head_first)
+    a = PoolArgs()
+    if grid is None:
+        blocks = (s + 127) // 128
+    else:
+        blocks = (grid[0] * grid[1] * grid[2] + 127) // 128 + (txt_len + 127) // 128
+        a.t, a.h, a.w = grid
+        a.txt_len, a.permute = txt_len, 1
+    pooled = torch.empty(b, n, blocks, d, dtype=torch.float32, device=x.device)
+    a.x, a.pooled = x.data_ptr(), pooled.data_ptr()
+    a.batch, a.heads, a.seq, a.head_dim = b, n, s, d
+    a.x_stride[:] = strides_bns(x, head_first)
+    a.dtype, a.block_size = dtype_code(x.dtype), 128
+    check(lib().mindiesd_rf_pool(C.byref(a), current_stream_ptr(x.device)), "mindiesd_rf_pool")
+    return pooled
+
+
+def fa_block_quant(x, row_block=128, head_first=True, per_channel=False, rotate=False):
+    b, n, s, d = _dims(x, head_first)
+    out = torch.empty(b, n, s, d, dtype=torch.float8_e4m3fn, device=x.device)
+    nscale = d if per_channel else (s + row_block - 1) // row_block
+    scales = torch.empty(b, n, nscale, dtype=torch.float32, device=x.device)
+    a = QuantArgs()
+    a.x, a.out, a.scales = x.data_ptr(), out.data_ptr(), scales.data_ptr()
+    a.batch, a.heads, a.seq, a.head_dim = b, n, s, d
+    a.x_stride[:] = strides_bns(x, head_first)
+    a.dtype, a.mode, a.row_block, a.rotate = dtype_code(x.dtype), int(per_channel), row_block, int(rotate)
+    check(lib().mindiesd_fa_block_quant(C.byref(a), current_stream_ptr(x.device)), "mindiesd_fa_block_quant")
+    return out, scales

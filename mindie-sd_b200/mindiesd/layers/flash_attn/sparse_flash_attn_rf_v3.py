@@ -1,0 +1,70 @@
+"""RainFusion v3: block-sparse attention from an int8 block mask, with mask reuse across steps
+(mindiesd/layers/flash_attn/sparse_flash_attn_rf_v3.py:22-295 of MindIE-SD)."""
+import torch
+
+from .. import _custom_ops as ops
+from ...utils.exception import ParametersInvalid
+
+
+def _bsa_inv_rearrange(out, tq, hq, wq, input_layout="BSND"):
+    """Back from window order to (t, h, w) raster order (no text tokens)."""
+    return torch.ops.mindiesd.rf_rearrange(out, [tq, hq, wq], 0, input_layout, True)
+
+
+def do_tensor_rearrange_only(q, k, v, txt_len, latent_shape_q, latent_shape_k, input_layout):
+    """Window permutation of q, k, v without pooling: what a step with a cached mask needs."""
+    grid = list(latent_shape_q)
+    return tuple(torch.ops.mindiesd.rf_rearrange(x, grid, int(txt_len), input_layout, False) for x in (q, k, v))
+
+
+def rain_fusion_attention_v3(query, key, value, block_sparse_mask, scale=None, head_num=None,
+                             num_key_value_heads=None, input_layout="BNSD", actual_seq_lengths=None,
+                             actual_seq_lengths_kv=None, sparse_size=128, inner_precise=4):
+    """softmax(scale q k^T over the kept 128x128 blocks) v.  The operator takes BNSD; a BSND input
+    is passed as a transposed view (the kernel reads through strides, so nothing is copied)."""
+    if scale is None:
+        scale = query.shape[-1] ** -0.5
+    if num_key_value_heads is None:
+        num_key_value_heads = head_num
+    if input_layout not in ("BNSD", "BSND"):
+        raise ParametersInvalid(f"The input_layout must in ['BSND', 'BNSD'], but got {input_layout}.")
+    permuted = input_layout == "BSND"
+    if permuted:
+        query, key, value = query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2)
+    out, _ = ops.block_sparse_attention(
+        query, key, value, block_sparse_mask=block_sparse_mask, block_shape=[sparse_size, sparse_size],
+        q_input_layout="BNSD", kv_input_layout="BNSD", num_key_value_heads=num_key_value_heads or 1,
+        scale_value=scale, inner_precise=inner_precise, actual_seq_lengths=actual_seq_lengths,
+        actual_seq_lengths_kv=actual_seq_lengths_kv, softmax_lse_flag=0)
+    return out.transpose(1, 2) if permuted else out
+
+
+def bsa_sparse_attention_v3(q, k, v, latent_shape_q, latent_shape_k=None, txt_len=0, pool_size=128, sparsity=0.5,
+                            input_layout="BSND", head_num=None, num_key_value_heads=None, scale=None,
+                            inner_precise=4, cached_mask=None, protect_first_frame=True, temporal_band=-1):
+    """rearrange -> mask -> block-sparse attention -> inverse rearrange.  Returns (out, mask); pass
+    the mask back as `cached_mask` on later steps to skip the mask builder.  `temporal_band` >= 0
+    additionally keeps block pairs whose frames lie within that distance (not in the reference)."""
+    if latent_shape_k is None:
+        latent_shape_k = latent_shape_q
+    if head_num is None:
+        head_num = q.shape[1] if input_layout == "BNSD" else q.shape[2]
+    if scale is None:
+        scale = float(q.shape[-1]) ** -0.5
+    grid = list(latent_shape_q)
+    if cached_mask is None:
+        # One fused launch pair on the un-permuted q and k: the permutation is index arithmetic.
+        new_mask, _, _ = torch.ops.mindiesd.rf_block_mask(
+            q, k, grid, int(txt_len), float(sparsity), float(scale), int(pool_size), input_layout,
+            bool(protect_first_frame), int(temporal_band), False)
+    else:
+        new_mask = cached_mask
+    q_, k_, v_ = do_tensor_rearrange_only(q, k, v, txt_len, latent_shape_q, latent_shape_k, input_layout)
+    s_dim = 2 if input_layout == "BNSD" else 1
+    lens = [q_.shape[s_dim]] * q_.shape[0]
+    out = rain_fusion_attention_v3(q_, k_, v_, new_mask, scale=scale, head_num=head_num,
+                                   num_key_value_heads=num_key_value_heads, input_layout=input_layout,
+                                   actual_seq_lengths=lens, actual_seq_lengths_kv=lens, sparse_size=pool_size,
+                                   inner_precise=inner_precise)
+    out = torch.ops.mindiesd.rf_rearrange(out, grid, int(txt_len), input_layout, True)
+    return out, new_mask

@@ -1,0 +1,158 @@
+"""GPU parity of the RainFusion kernels through the C ABI: permutation, pooled means, block mask
+(bit-exact against the vectors of the reference and against the oracle) and block-sparse attention."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import inputs
+from oracle import attention as oa
+from oracle import rainfusion as orf
+
+pytestmark = pytest.mark.gpu
+G = Path(__file__).resolve().parent / "golden"
+
+
+def _unpack(z, name):
+    shape = tuple(z[f"{name}_mask_shape"])
+    return np.unpackbits(z[f"{name}_mask_bits"])[:int(np.prod(shape))].reshape(shape).astype(np.int8)
+
+
+@pytest.mark.parametrize("grid", inputs.PERM_GRIDS + [(21, 30, 52)])
+@pytest.mark.parametrize("head_first", [True, False])
+def test_permutation_bit_exact(grid, head_first):
+    from mindiesd import _cabi
+    t, h, w = grid
+    for txt in (0, 77):
+        s = t * h * w + txt
+        x = inputs.randn(5, 1, 2, s, 16, dtype=torch.bfloat16)
+        layout = "BNSD" if head_first else "BSND"
+        if not head_first:
+            x = x.transpose(1, 2).contiguous()
+        y = _cabi.rf_rearrange(x.cuda(), grid, txt, head_first)
+        assert torch.equal(y.cpu(), orf.rearrange(x, grid, txt, layout))
+        back = _cabi.rf_rearrange(y, grid, txt, head_first, inverse=True)
+        assert torch.equal(back.cpu(), x)
+    # 4-byte elements
+    x = inputs.randn(6, 1, 1, t * h * w, 8)
+    y = _cabi.rf_rearrange(x.cuda(), grid, 0, True)
+    assert torch.equal(y.cpu(), orf.rearrange(x, grid, 0, "BNSD"))
+    assert _cabi.device_status() == 0
+
+
+def test_ragged_small_grid_is_rejected():
+    from mindiesd import _cabi
+    x = torch.zeros(1, 1, 3 * 5 * 7, 16, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(_cabi.NativeLibraryError):
+        _cabi.rf_rearrange(x, (3, 5, 7), 0, True)  # the reference's permutation is undefined there
+
+
+def test_pooled_means():
+    from mindiesd import _cabi
+    z = np.load(G / "avgpool.npz")
+    x = inputs.randn(3, 1, 2, 300, 16)
+    got = _cabi.rf_pool(x.cuda(), None, 0, True).cpu()
+    assert (got - torch.from_numpy(z["bnsd"])).abs().max().item() < 1e-6  # the reference accumulates in fp32
+    grid, txt = (3, 30, 52), 200
+    q, _ = inputs.structured_qk(16, 2, grid, 128, txt)
+    want, _ = orf.pooled_means(q.double(), q.double(), grid, txt, 128, "BNSD")
+    got = _cabi.rf_pool(q.cuda(), grid, txt, True).cpu()
+    assert got.shape == want.shape
+    assert torch.equal(got, want.float())  # exact sum, one rounding
+
+
+@pytest.mark.parametrize("case", inputs.MASK_CASES, ids=[c[0] for c in inputs.MASK_CASES])
+def test_block_mask_bit_exact(case):
+    """0 differing bits against the mask the reference produced from the fp32 upcast of the same
+    bf16 data; the compacted lists equal the reference's too."""
+    from mindiesd import _cabi
+    name, grid, txt, heads, dim, sparsity, layout, seed = case
+    z = np.load(G / "mask.npz")
+    want = _unpack(z, name)
+    q, k = inputs.structured_qk(seed, heads, grid, dim, txt)
+    head_first = layout == "BNSD"
+    if not head_first:
+        q, k = q.transpose(1, 2).contiguous(), k.transpose(1, 2).contiguous()
+    mask, sel, num = _cabi.rf_block_mask(q.cuda(), k.cuda(), grid, txt, sparsity, head_first, want_lists=True)
+    diff = int((mask.cpu().numpy() != want).sum())
+    assert diff == 0, f"{diff} of {want.size} mask bits differ (min margin {z.get(name + '_min_margin')})"
+    sel_o, num_o = orf.select_lists(torch.from_numpy(want))
+    assert torch.equal(sel.cpu(), sel_o) and torch.equal(num.cpu(), num_o)
+    if f"{name}_select_idx" in z.files:
+        assert np.array_equal(sel.cpu().numpy(), z[f"{name}_select_idx"].astype(np.int64))
+    # fp32 inputs take the same path
+    mask32 = _cabi.rf_block_mask(q.float().cuda(), k.float().cuda(), grid, txt, sparsity, head_first)
+    assert torch.equal(mask32, mask)
+    assert _cabi.device_status() == 0
+
+
+def test_temporal_band_and_first_frame_switch():
+    from mindiesd import _cabi
+    grid = (4, 16, 24)
+    q, k = inputs.structured_qk(33, 2, grid, 128)
+    base = _cabi.rf_block_mask(q.cuda(), k.cuda(), grid, 0, 0.75, True, protect_first_frame=False).cpu()
+    prot = _cabi.rf_block_mask(q.cuda(), k.cuda(), grid, 0, 0.75, True, protect_first_frame=True).cpu()
+    fb = (16 * 24 + 127) // 128
+    assert prot[:, :, :fb].all() and prot[:, :, :, :fb].all()
+    assert torch.equal(prot[:, :, fb:, fb:], base[:, :, fb:, fb:])
+    band = _cabi.rf_block_mask(q.cuda(), k.cuda(), grid, 0, 0.75, True, protect_first_frame=True, temporal_band=1).cpu()
+    want = prot.bool() | torch.from_numpy(orf.temporal_band(grid, 0, 1))[None, None]
+    assert torch.equal(band.bool(), want)
+
+
+def test_block_sparse_attention_matches_reference_vectors():
+    from mindiesd import _cabi
+    z = np.load(G / "block_sparse.npz")
+    q, k, v = (inputs.randn(31 + i, 1, 2, 300, 128, dtype=torch.bfloat16) for i in range(3))
+    mask = torch.from_numpy(z["mask"]).cuda()
+    out, lse = _cabi.attention(q.cuda(), k.cuda(), v.cuda(), block_mask=mask, out_dtype=torch.float32, want_lse=True)
+    want = torch.from_numpy(z["out"])
+    eb, ok, mx = oa.ref_compare(want, out.cpu(), 2 ** -6)  # the tolerance of the reference's own test
+    assert ok, (eb, mx)
+    assert torch.count_nonzero(out[0, 0, 128:256]) == 0 and torch.isinf(lse[0, 0, 128:256]).all()
+
+
+@pytest.mark.parametrize("head_first", [True, False])
+def test_block_sparse_mask_and_list_agree_with_oracle(head_first):
+    from mindiesd import _cabi
+    b, n, s = 2, 3, 1500
+    shape = (b, n, s, 128) if head_first else (b, s, n, 128)
+    q, k, v = (inputs.randn(70 + i, *shape, dtype=torch.bfloat16) for i in range(3))
+    nb = (s + 127) // 128
+    m = (np.random.RandomState(9).rand(1, n, nb, nb) < 0.35)
+    m[:, :, np.arange(nb), np.arange(nb)] = True
+    mask = torch.from_numpy(np.repeat(m, b, 0).astype(np.int8))
+    to_bnsd = (lambda x: x) if head_first else (lambda x: x.transpose(1, 2))
+    want = oa.block_sparse_attention(to_bnsd(q), to_bnsd(k), to_bnsd(v), mask.numpy())
+    out = _cabi.attention(q.cuda(), k.cuda(), v.cuda(), head_first=head_first, block_mask=mask.cuda())
+    diff = (to_bnsd(out).float().cpu() - want).abs()
+    assert diff.max().item() <= 2e-2 and diff.mean().item() <= 2e-3
+    sel, num = orf.select_lists(mask)
+    out2 = _cabi.attention(q.cuda(), k.cuda(), v.cuda(), head_first=head_first, select_idx=sel.cuda(),
+                           select_num=num.cuda())
+    assert torch.equal(out2, out)  # the list walk visits the same blocks in the same order
+    assert _cabi.device_status() == 0
+
+
+def test_full_mask_equals_dense():
+    from mindiesd import _cabi
+    q, k, v = (inputs.randn(80 + i, 1, 2, 900, 128, dtype=torch.bfloat16).cuda() for i in range(3))
+    mask = torch.ones(1, 2, 8, 8, dtype=torch.int8, device="cuda")
+    assert torch.equal(_cabi.attention(q, k, v, block_mask=mask), _cabi.attention(q, k, v))
+
+
+def test_wan_720p_mask_density():
+    """Config C3 grid (21x45x80, 591 blocks), sparsity 0.75, on 2 heads generated on the device:
+    every row keeps at least ceil(591/4) = 148 blocks plus the 29 first-frame columns, and the
+    device mask equals the oracle run on the same data copied to the host."""
+    import workloads
+    from mindiesd import _cabi
+    q, k, _ = workloads.make_qkv(workloads.C3, "cuda", seed=4, heads=2)
+    mask = _cabi.rf_block_mask(q, k, workloads.C3.grid, 0, 0.75, True).cpu()
+    assert mask.shape == (1, 2, 591, 591)
+    kept = mask[:, :, 29:].sum(-1)
+    assert kept.min().item() >= 148 and 0.30 < mask.float().mean().item() < 0.36
+    qp, kp = orf.pooled_means(q.cpu().float(), k.cpu().float(), workloads.C3.grid, 0, 128, "BNSD")
+    want = orf.blockwise_mask(qp, kp, 0, 0.75, 128 ** -0.5, 128, workloads.C3.grid, "BNSD")
+    assert int((mask != want).sum()) == 0

@@ -1,0 +1,127 @@
+"""Pins the CPU oracle against vectors produced by MindIE-SD's own Python code
+(tests/golden/make_golden.py).  CPU only."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import inputs
+from oracle import attention as oa
+from oracle import rainfusion as orf
+
+G = Path(__file__).resolve().parent / "golden"
+
+
+def _unpack(z, name):
+    shape = tuple(z[f"{name}_mask_shape"])
+    n = int(np.prod(shape))
+    return np.unpackbits(z[f"{name}_mask_bits"])[:n].reshape(shape).astype(np.int8)
+
+
+def test_permutation_matches_reference():
+    z = np.load(G / "permutation.npz")
+    for (t, h, w) in inputs.PERM_GRIDS:
+        src = orf.window_permutation(t, h, w)
+        for layout in ("BNSD", "BSND"):
+            assert np.array_equal(src, z[f"{t}x{h}x{w}_{layout}"].astype(np.int64)), (t, h, w, layout)
+        assert np.array_equal(np.sort(src), np.arange(t * h * w))
+
+
+@pytest.mark.parametrize("layout", ["BNSD", "BSND"])
+def test_rearrange_round_trip(layout):
+    for (t, h, w) in inputs.PERM_GRIDS[:4]:
+        for txt in (0, 37):
+            s = t * h * w + txt
+            x = inputs.randn(1, 1, 2, s, 8)
+            if layout == "BSND":
+                x = x.transpose(1, 2).contiguous()
+            y = orf.rearrange(x, (t, h, w), txt, layout)
+            assert torch.equal(orf.inv_rearrange(y, (t, h, w), txt, layout), x)
+            dim = 2 if layout == "BNSD" else 1
+            if txt:  # text moves from the front to the back
+                assert torch.equal(y.narrow(dim, s - txt, txt), x.narrow(dim, 0, txt))
+
+
+def test_avgpool_matches_reference():
+    z = np.load(G / "avgpool.npz")
+    x = inputs.randn(3, 1, 2, 300, 16)
+    assert np.array_equal(orf.avgpool(x, 128, "BNSD").numpy(), z["bnsd"])
+    assert np.array_equal(orf.avgpool(x.transpose(1, 2).contiguous(), 128, "BSND").numpy(), z["bsnd"])
+    # known answer of the reference's own test: block means of 0..255
+    t = torch.arange(256, dtype=torch.float32).reshape(1, 1, 256, 1)
+    out = orf.avgpool(t, 128, "BNSD")
+    assert abs(out[0, 0, 0, 0].item() - 63.5) < 1e-4 and abs(out[0, 0, 1, 0].item() - 191.5) < 1e-4
+    assert orf.avgpool(torch.ones(1, 1, 64, 4), 128, "BNSD").shape == (1, 1, 1, 4)  # tail only
+
+
+@pytest.mark.parametrize("case", inputs.MASK_CASES, ids=[c[0] for c in inputs.MASK_CASES])
+def test_blockwise_mask_matches_reference(case):
+    name, grid, txt, heads, dim, sparsity, layout, seed = case
+    z = np.load(G / "mask.npz")
+    want = _unpack(z, name)
+    q, k = inputs.structured_qk(seed, heads, grid, dim, txt)
+    q, k = q.float(), k.float()
+    if layout == "BSND":
+        q, k = q.transpose(1, 2).contiguous(), k.transpose(1, 2).contiguous()
+    qp, kp = orf.pooled_means(q, k, grid, txt, 128, layout)
+    if f"{name}_qpool" in z.files:
+        assert np.array_equal(qp.numpy(), z[f"{name}_qpool"])
+    scale = dim ** -0.5
+    got = orf.blockwise_mask(qp, kp, txt, sparsity, scale, 128, grid, layout)
+    assert np.array_equal(got.numpy(), want)
+    # thresholding the raw float64 scores keeps the same set (the softmax is monotone per row)
+    raw = orf.blockwise_mask(qp, kp, txt, sparsity, scale, 128, grid, layout, use_softmax=False)
+    assert np.array_equal(raw.numpy(), want)
+    if f"{name}_select_idx" in z.files:
+        sel, num = orf.select_lists(got)
+        assert np.array_equal(sel.numpy(), z[f"{name}_select_idx"].astype(np.int64))
+        assert np.array_equal(num.numpy(), z[f"{name}_select_num"].astype(np.int64))
+
+
+def test_mask_index_matches_reference():
+    z = np.load(G / "mask_index.npz")
+    idx, num = orf.mask_index(z["mask"])
+    assert np.array_equal(idx.numpy(), z["index"].astype(np.int64))
+    assert np.array_equal(num.numpy(), z["mask"].sum(-1))
+    # known answers of the reference's own test
+    m = np.zeros((1, 1, 4, 4), dtype=bool)
+    m[0, 0, 0, 0] = m[0, 0, 0, 2] = True
+    idx, _ = orf.mask_index(m)
+    assert idx[0, 0, 0].tolist() == [0, 2, -1, -1]
+    idx, _ = orf.mask_index(np.ones((1, 1, 4, 4), dtype=bool))
+    assert idx[0, 0, 3].tolist() == [0, 1, 2, 3]
+
+
+def test_dense_attention_matches_reference():
+    z = np.load(G / "dense.npz")
+    for tag, dtype, head_first, sq, skv in (("fp32_bnsd", torch.float32, True, 200, 200),
+                                            ("bf16_bsnd", torch.bfloat16, False, 160, 333),
+                                            ("fp16_bnsd", torch.float16, True, 130, 257)):
+        shape_q = (1, 2, sq, 128) if head_first else (1, sq, 2, 128)
+        shape_k = (1, 2, skv, 128) if head_first else (1, skv, 2, 128)
+        q, k, v = inputs.randn(21, *shape_q, dtype=dtype), inputs.randn(22, *shape_k, dtype=dtype), \
+            inputs.randn(23, *shape_k, dtype=dtype)
+        want = torch.from_numpy(z[tag])
+        got = oa.attention_math(q, k, v, head_first=head_first).float()
+        assert torch.equal(got, want), tag
+        chunked = oa.attention_math_chunked(q, k, v, head_first=head_first, rows=64).float()
+        tol = 0 if dtype == torch.float32 else 2e-2  # chunking may change the blocking of the low-precision GEMM
+        assert (chunked - want).abs().max().item() <= max(tol, 1e-6), tag
+
+
+def test_block_sparse_attention_matches_reference():
+    z = np.load(G / "block_sparse.npz")
+    q, k, v = (inputs.randn(31 + i, 1, 2, 300, 128, dtype=torch.bfloat16) for i in range(3))
+    got = oa.block_sparse_attention(q, k, v, z["mask"], 128)
+    want = torch.from_numpy(z["out"])
+    assert (got - want).abs().max().item() < 1e-6
+    assert torch.count_nonzero(want[0, 0, 128:256]) == 0  # the row that keeps nothing
+    assert oa.ref_compare(want, got, 2 ** -6)[1]
+
+
+def test_temporal_band_extension():
+    band = orf.temporal_band((4, 16, 16), 0, 1)  # 256 tokens per frame, two blocks per frame
+    assert band.shape == (8, 8)
+    assert band[0, 3] and not band[0, 4] and band[7, 4] and not band[7, 3]
+    assert np.array_equal(band, band.T)
