@@ -1,0 +1,385 @@
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+A step is one self-attention layer of the Wan2.1-14B 720p shape (B1 N40 S75600 D128, bf16, dense):
+117.05 TFLOP.  N = 1 runs the dense tcgen05 kernel on one GPU; N > 1 (under torchrun, one rank per
+GPU) runs the same layer sequence-parallel with the Ulysses wrapper, so the total work is fixed
+("strong" scaling) and `value` is the whole job's dense-equivalent TFLOP/s.  Rank 0 prints one JSON
+line.  Inputs are seeded synthetic tensors of the named shapes (no dataset exists for this path);
+3.1 GB of operands per step exceed the 126 MB L2, so no L2 flush is needed between steps.
+
+Other single-GPU workloads of the same path (`--workload sparse|fp8|mask|quant|rearrange|c2`) print the
+same kind of line for their kernel; `--impl reference` times the CPU oracle (the reference's
+unfused torch formula) on the host cores for the same metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (ROOT, ROOT / "mindie-sd_b200", ROOT / "tests" / "golden"):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+import torch  # noqa: E402
+
+HEAD_DIM = 128
+# DRAM bytes one launch of the dense kernel moves at the benchmark shape, from one ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture has been taken.
+DENSE_DRAM_TRAFFIC_BYTES = None
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            d = json.loads(path.read_text())
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def physical_gpu_index(local_index):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        ids = [x for x in vis.split(",") if x != ""]
+        if local_index < len(ids) and ids[local_index].isdigit():
+            return int(ids[local_index])
+    return local_index
+
+
+def timed(fn, steps, warmup, barrier=None):
+    """Runs fn() warmup + steps times; returns elapsed milliseconds of the timed steps on the
+    current stream (CUDA events, synchronised on both sides)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return e0.elapsed_time(e1)
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU oracle legs
+# ---------------------------------------------------------------------------------------------------
+def cpu_attention_sample(seq, target_seconds=12.0, repeats=1):
+    """The reference's unfused attention formula on the host cores for one head and a block of
+    query rows against the full key/value sequence (fp32 on bf16-rounded values).  The block is
+    sized from a short probe so that the timed part takes about target_seconds."""
+    from oracle import attention as oa
+    g = torch.Generator().manual_seed(1234)
+    k = (0.5 * torch.randn(1, 1, seq, HEAD_DIM, generator=g)).bfloat16().float()
+    v = (0.5 * torch.randn(1, 1, seq, HEAD_DIM, generator=g)).bfloat16().float()
+
+    def run(rows):
+        q = (0.5 * torch.randn(1, 1, rows, HEAD_DIM, generator=g)).bfloat16().float()
+        t0 = time.perf_counter()
+        oa.attention_math_chunked(q, k, v, head_first=True, rows=1024)
+        return time.perf_counter() - t0
+
+    run(256)
+    probe = run(1024)
+    rows = int(min(seq, max(1024, 1024 * target_seconds / max(probe, 1e-6))))
+    rows -= rows % 128 or 0
+    best = min(run(rows) for _ in range(repeats))
+    flops = 4.0 * rows * seq * HEAD_DIM
+    return {"value": flops / best / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"1 head x {rows} query rows x {seq} keys, fp32 on bf16-rounded values, {best:.2f} s"}, best, flops
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    seq = 75600
+    times, flops = [], 0.0
+    info = None
+    for i in range(args.warmup + args.steps):
+        info, t, flops = cpu_attention_sample(seq, target_seconds=6.0)
+        if i >= args.warmup:
+            times.append(t)
+    value = flops * len(times) / sum(times) / 1e12
+    info["value"] = value
+    line = {
+        "impl": "reference", "metric": "attention_dense_equiv_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * 75600.0 * 75600 * 40 * 4 * HEAD_DIM / (value * 1e12),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "wan2.1-14b-720p dense self-attention, B1 N40 S75600 D128",
+                   "note": "CPU oracle (the reference's unfused torch formula) on the host cores; each step is a "
+                           "bounded sample; ms_per_step is the full layer extrapolated by FLOPs"},
+        "cpu_baseline": info,
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+# GPU workloads
+# ---------------------------------------------------------------------------------------------------
+def dense_or_ulysses(args, rank, world, device):
+    import workloads
+    from mindiesd import _cabi, attention_forward, ulysses_attention
+    import torch.distributed as dist
+
+    cfg = workloads.C3
+    q, k, v = workloads.make_qkv(cfg, device, seed=0, layout="BSND")  # [1, S, 40, 128]
+    s_loc = cfg.seq // world
+    if world > 1:
+        q, k, v = (x[:, rank * s_loc:(rank + 1) * s_loc].contiguous() for x in (q, k, v))
+    torch.cuda.empty_cache()
+    barrier = (lambda: dist.barrier()) if world > 1 else None
+    launches_per_step = 1
+    if world == 1:
+        out = torch.empty_like(q)
+        step = lambda: _cabi.attention(q, k, v, head_first=False, out=out)  # noqa: E731
+    else:
+        chunks = min(cfg.heads // world, 8)
+        launches_per_step = chunks
+        step = lambda: ulysses_attention(q, k, v, head_chunks=chunks)  # noqa: E731
+
+    sampler = ClockSampler(physical_gpu_index(device.index))
+    sampler.start()
+    ms = timed(step, args.steps, args.warmup, barrier)
+    clocks = sampler.stop()
+
+    # End to end through the public Python API with host buffers: every step copies this rank's
+    # q, k, v from pinned host memory and reads its output back.
+    hq, hk, hv = (torch.empty(x.shape, dtype=x.dtype, pin_memory=True).copy_(x) for x in (q, k, v))
+    ho = torch.empty(q.shape, dtype=q.dtype, pin_memory=True)
+
+    def e2e_step():
+        dq, dk, dv = (h.to(device, non_blocking=True) for h in (hq, hk, hv))
+        if world == 1:
+            o = attention_forward(dq, dk, dv, head_first=False)
+        else:
+            o = ulysses_attention(dq, dk, dv, head_chunks=launches_per_step)
+        ho.copy_(o, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_ms = timed(e2e_step, e2e_steps, 1, barrier)
+
+    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
+    status = _cabi.device_status()
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    ms_step = ms / args.steps
+    value = cfg.flops / (ms_step * 1e-3) / 1e12
+    line = {
+        "metric": "attention_dense_equiv_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "wan2.1-14b-720p dense self-attention, B1 N40 S75600 D128 (21x45x80 latent grid)",
+                   "layout": "BSND", "parallelism": "single GPU" if world == 1 else f"ulysses sp{world}, {launches_per_step} head chunks",
+                   "flops_per_step": cfg.flops, "l2": "operands (3.1 GB per step) exceed L2; no flush",
+                   "tflops_per_gpu": value / world, "kernel_status": status},
+        "clocks": clocks,
+        "e2e": {"value": cfg.flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": 3 * q.numel() * q.element_size() * world,
+                "d2h_bytes_per_step": q.numel() * q.element_size() * world,
+                "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
+                "api": "mindiesd.attention_forward" if world == 1 else "mindiesd.ulysses_attention"},
+        "gpu_launches": launches_per_step * args.steps,
+    }
+    if world == 1:
+        peak = peaks["bf16_tflops_sustained"]
+        line["roofline"] = {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak,
+                            "traffic": DENSE_DRAM_TRAFFIC_BYTES, "peak_source": peaks["source"] + " cuBLAS bf16, sustained",
+                            "frac_of_burst": value / peaks["bf16_tflops"], "frac_of_nominal_2250": value / 2250.0,
+                            "kernel": "fa_fwd_kernel<bf16>", "flops_per_launch": cfg.flops}
+        cpu, _, _ = cpu_attention_sample(cfg.seq, target_seconds=12.0)
+        line["cpu_baseline"] = cpu
+    return line
+
+
+def single_gpu_workload(args, device):
+    """Secondary kernels of the path at the benchmark shape; each prints the same kind of line."""
+    import workloads
+    from mindiesd import _cabi
+    cfg = workloads.C3
+    peaks = measured_peaks()
+    name = args.workload
+    q, k, v = workloads.make_qkv(workloads.C4 if name in ("fp8", "quant") else (workloads.C2 if name == "c2" else cfg),
+                                 device, seed=0)
+    launches, bound, extra = 1, "tensor", {}
+    if name == "c2":
+        cfg = workloads.C2
+        out = torch.empty_like(q)
+        step = lambda: _cabi.attention(q, k, v, out=out)  # noqa: E731
+        work, unit = cfg.flops, "TFLOP/s"
+        label = "wan2.1-1.3b dense self-attention, B1 N12 S32760 D128, 3-D RoPE on q,k"
+    elif name == "sparse":
+        mask = _cabi.rf_block_mask(q, k, cfg.grid, 0, args.sparsity, True, temporal_band=args.band)
+        qr, kr, vr = (_cabi.rf_rearrange(x, cfg.grid, 0, True) for x in (q, k, v))
+        del q, k, v
+        out = torch.empty_like(qr)
+        step = lambda: _cabi.attention(qr, kr, vr, block_mask=mask, out=out)  # noqa: E731
+        density = mask.float().mean().item()
+        work, unit = cfg.flops, "TFLOP/s"
+        extra = {"block_density": density, "sparsity_arg": args.sparsity, "temporal_band": args.band,
+                 "executed_tflop": cfg.flops * density / 1e12}
+        label = "RainFusion block-sparse attention (mask prebuilt, tokens pre-permuted), B1 N40 S75600 D128"
+    elif name == "fp8":
+        q8, qs = _cabi.fa_block_quant(q, 128, rotate=True)
+        k8, ks = _cabi.fa_block_quant(k, 128, rotate=True)
+        v8, vs = _cabi.fa_block_quant(v, per_channel=True)
+        del q, k, v
+        out = torch.empty(q8.shape, dtype=torch.bfloat16, device=device)
+        step = lambda: _cabi.attention(q8, k8, v8, q_scale=qs, k_scale=ks, v_scale=vs, k_scale_block=128,  # noqa: E731
+                                       v_scale_block=0, out=out)
+        work, unit = cfg.flops, "TFLOP/s"
+        label = "FP8-e4m3 attention (operands pre-quantised), B1 N40 S75600 D128"
+    elif name == "mask":
+        scratch = torch.empty(_cabi.lib().mindiesd_rf_block_mask_scratch_bytes(1, cfg.heads, cfg.seq, HEAD_DIM),
+                              dtype=torch.uint8, device=device)
+        step = lambda: _cabi.rf_block_mask(q, k, cfg.grid, 0, 0.75, True, scratch=scratch)  # noqa: E731
+        work = 2.0 * q.numel() * 2 + cfg.heads * 591 * 591  # read q and k once, write the int8 mask
+        unit, bound, launches = "GB/s", "hbm", 2
+        label = "RainFusion mask builder (pool + mask kernels), B1 N40 S75600 D128, sparsity 0.75"
+    elif name == "quant":
+        step = lambda: _cabi.fa_block_quant(q, 128, rotate=True)  # noqa: E731
+        work = q.numel() * 3.0  # 2 bytes in, 1 byte out per element
+        unit, bound = "GB/s", "hbm"
+        label = "e4m3 block quantisation with Hadamard rotation of one operand, B1 N40 S75600 D128"
+    elif name == "rearrange":
+        step = lambda: _cabi.rf_rearrange(q, cfg.grid, 0, True)  # noqa: E731
+        work = q.numel() * 4.0
+        unit, bound = "GB/s", "hbm"
+        label = "RainFusion window permutation of one operand, B1 N40 S75600 D128"
+    else:
+        raise SystemExit(f"unknown workload {name}")
+    sampler = ClockSampler(physical_gpu_index(device.index))
+    sampler.start()
+    ms = timed(step, args.steps, args.warmup)
+    clocks = sampler.stop()
+    ms_step = ms / args.steps
+    value = work / (ms_step * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    peak = peaks["bf16_tflops_sustained"] if bound == "tensor" else peaks["hbm_gbs"]
+    return {
+        "metric": "attention_dense_equiv_tflops" if unit == "TFLOP/s" else "achieved_hbm_gbs", "value": value,
+        "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "e4m3" if name == "fp8" else "bf16", "data": "synthetic",
+        "config": dict({"workload": label, "l2": "operands exceed L2; no flush", "kernel_status": _cabi.device_status()}, **extra),
+        "clocks": clocks,
+        "roofline": {"bound": bound, "achieved": value, "peak": peak, "unit": unit, "frac": value / peak, "traffic": None,
+                     "peak_source": peaks["source"]},
+        "gpu_launches": launches * args.steps,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="dense")
+    ap.add_argument("--sparsity", type=float, default=0.75)
+    ap.add_argument("--band", type=int, default=-1)
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "b200":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU implementation")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    try:
+        if args.workload == "dense" or world > 1:
+            line = dense_or_ulysses(args, rank, world, device)
+        else:
+            line = single_gpu_workload(args, device)
+        if rank == 0 and line is not None:
+            print(json.dumps(line), flush=True)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
