@@ -160,6 +160,26 @@ size_t mindiesd_rf_block_mask_scratch_bytes(int32_t batch, int32_t heads, int32_
 int mindiesd_rf_block_mask(const mindiesd_mask_args* args, void* stream);
 
 /*
+ * The same mask builder for hosts that cannot allocate device memory.  It has no counterpart in
+ * the reference, whose operators take a fresh workspace tensor from the framework on every call.
+ * Some hosts of this library cannot do the equivalent: a C or C++ service that handed the whole
+ * device to its own arena at start-up and forbids cudaMalloc afterwards, or a step loop in which a
+ * cudaMalloc would stall the device.  For them the pooled means live in a 4 MiB array inside the
+ * library's device image (every GPU that loads the library holds those 4 MiB until the process
+ * exits); `scratch` and `scratch_bytes` of the arguments are ignored and the call allocates nothing.
+ *
+ * Limit: batch * heads * blocks * head_dim * 2 * sizeof(float) must fit in
+ * mindiesd_rf_block_mask_static_capacity() bytes (blocks = ceil(t*h*w/128) + ceil(txt_len/128));
+ * a larger problem returns MINDIESD_E_CAPACITY and must use mindiesd_rf_block_mask.
+ * The first call on each device looks up the array's device address (the only set-up); make that
+ * call before starting any stream capture.  All calls on a device share the one array: calls whose
+ * kernels may overlap on the GPU (different streams without ordering) race and give wrong masks;
+ * calls on one stream, or otherwise ordered, are safe.  Nothing needs clearing between calls.
+ */
+size_t mindiesd_rf_block_mask_static_capacity(void);
+int mindiesd_rf_block_mask_static(const mindiesd_mask_args* args, void* stream);
+
+/*
  * The two stages of the mask builder on their own, for callers that use the reference's helper
  * functions one at a time.
  *

@@ -293,3 +293,32 @@ def fa_block_quant(x, row_block=128, head_first=True, per_channel=False, rotate=
     a.dtype, a.mode, a.row_block, a.rotate = dtype_code(x.dtype), int(per_channel), row_block, int(rotate)
     check(lib().mindiesd_fa_block_quant(C.byref(a), current_stream_ptr(x.device)), "mindiesd_fa_block_quant")
     return out, scales
+
+
+def rf_block_mask_static(q, k, grid, txt_len=0, sparsity=0.0, head_first=True, protect_first_frame=True,
+                         temporal_band=-1, want_lists=False):
+    """mindiesd_rf_block_mask_static: the mask builder with its scratch inside the library, for hosts
+    that may not allocate device memory.  Outputs are still the caller's; sizes beyond the library's
+    fixed 4 MiB of scratch raise NativeLibraryError (capacity)."""
+    fn = lib().mindiesd_rf_block_mask_static
+    fn.restype, fn.argtypes = C.c_int, [C.c_void_p, C.c_void_p]
+    b, n, s, d = _dims(q, head_first)
+    blocks = (grid[0] * grid[1] * grid[2] + 127) // 128 + (txt_len + 127) // 128
+    mask = torch.empty(b, n, blocks, blocks, dtype=torch.int8, device=q.device)
+    a = MaskArgs()
+    a.q, a.k = q.data_ptr(), k.data_ptr()
+    a.batch, a.heads, a.seq, a.head_dim = b, n, s, d
+    a.q_stride[:] = strides_bns(q, head_first)
+    a.k_stride[:] = strides_bns(k, head_first)
+    a.dtype = dtype_code(q.dtype)
+    a.t, a.h, a.w = grid
+    a.txt_len, a.block_size, a.scale, a.sparsity = txt_len, 128, d ** -0.5, float(sparsity)
+    a.protect_first_frame, a.temporal_band = int(protect_first_frame), temporal_band
+    a.mask = mask.data_ptr()
+    sel = num = None
+    if want_lists:
+        sel = torch.empty(blocks, n, blocks, dtype=torch.int64, device=q.device)
+        num = torch.empty(blocks, n, dtype=torch.int64, device=q.device)
+        a.select_idx, a.select_num = sel.data_ptr(), num.data_ptr()
+    check(fn(C.byref(a), current_stream_ptr(q.device)), "mindiesd_rf_block_mask_static")
+    return (mask, sel, num) if want_lists else mask
