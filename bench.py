@@ -193,6 +193,8 @@ def dense_or_ulysses(args, rank, world, device):
     import torch.distributed as dist
 
     cfg = workloads.C3
+    if args.heads:  # reduced head count: only for short profiler captures, named in the output
+        cfg = workloads.Config(cfg.name, cfg.batch, args.heads, cfg.grid, cfg.seq, cfg.dtype)
     q, k, v = workloads.make_qkv(cfg, device, seed=0, layout="BSND")  # [1, S, 40, 128]
     s_loc = cfg.seq // world
     if world > 1:
@@ -227,7 +229,7 @@ def dense_or_ulysses(args, rank, world, device):
         ho.copy_(o, non_blocking=True)
 
     e2e_steps = max(1, min(args.steps, 5))
-    e2e_ms = timed(e2e_step, e2e_steps, 1, barrier)
+    e2e_ms = timed(e2e_step, e2e_steps, 1, barrier) if not args.kernel_only else float("nan")
 
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
     if world > 1:
@@ -243,7 +245,7 @@ def dense_or_ulysses(args, rank, world, device):
         "metric": "attention_dense_equiv_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "wan2.1-14b-720p dense self-attention, B1 N40 S75600 D128 (21x45x80 latent grid)",
+        "config": {"workload": f"wan2.1-14b-720p dense self-attention, B1 N{cfg.heads} S75600 D128 (21x45x80 latent grid)",
                    "layout": "BSND", "parallelism": "single GPU" if world == 1 else f"ulysses sp{world}, {launches_per_step} head chunks",
                    "flops_per_step": cfg.flops, "l2": "operands (3.1 GB per step) exceed L2; no flush",
                    "tflops_per_gpu": value / world, "kernel_status": status},
@@ -261,8 +263,9 @@ def dense_or_ulysses(args, rank, world, device):
                             "traffic": DENSE_DRAM_TRAFFIC_BYTES, "peak_source": peaks["source"] + " cuBLAS bf16, sustained",
                             "frac_of_burst": value / peaks["bf16_tflops"], "frac_of_nominal_2250": value / 2250.0,
                             "kernel": "fa_fwd_kernel<bf16>", "flops_per_launch": cfg.flops}
-        cpu, _, _ = cpu_attention_sample(cfg.seq, target_seconds=12.0)
-        line["cpu_baseline"] = cpu
+        if not args.kernel_only:
+            cpu, _, _ = cpu_attention_sample(cfg.seq, target_seconds=12.0)
+            line["cpu_baseline"] = cpu
     return line
 
 
@@ -273,8 +276,10 @@ def single_gpu_workload(args, device):
     cfg = workloads.C3
     peaks = measured_peaks()
     name = args.workload
-    q, k, v = workloads.make_qkv(workloads.C4 if name in ("fp8", "quant") else (workloads.C2 if name == "c2" else cfg),
-                                 device, seed=0)
+    src = workloads.C4 if name in ("fp8", "quant") else (workloads.C2 if name == "c2" else cfg)
+    if args.heads:
+        cfg = workloads.Config(cfg.name, cfg.batch, args.heads, cfg.grid, cfg.seq, cfg.dtype)
+    q, k, v = workloads.make_qkv(src, device, seed=0, heads=args.heads or None)
     launches, bound, extra = 1, "tensor", {}
     if name == "c2":
         cfg = workloads.C2
@@ -334,7 +339,7 @@ def single_gpu_workload(args, device):
         "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "e4m3" if name == "fp8" else "bf16", "data": "synthetic",
-        "config": dict({"workload": label, "l2": "operands exceed L2; no flush", "kernel_status": _cabi.device_status()}, **extra),
+        "config": dict({"workload": label + (f" [heads reduced to {args.heads}]" if args.heads else ""), "l2": "operands exceed L2; no flush", "kernel_status": _cabi.device_status()}, **extra),
         "clocks": clocks,
         "roofline": {"bound": bound, "achieved": value, "peak": peak, "unit": unit, "frac": value / peak, "traffic": None,
                      "peak_source": peaks["source"]},
@@ -351,6 +356,8 @@ def main():
     ap.add_argument("--workload", default="dense")
     ap.add_argument("--sparsity", type=float, default=0.75)
     ap.add_argument("--band", type=int, default=-1)
+    ap.add_argument("--heads", type=int, default=0, help="reduced head count for profiler captures (default: the full 40)")
+    ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs (profiler captures)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "b200":
         args.warmup = 3

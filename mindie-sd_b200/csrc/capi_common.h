@@ -8,7 +8,7 @@
 
 namespace sdb {
 
-constexpr int kMaxMaskBlocks = 4096;  // 128-token blocks per sequence the mask builder accepts
+constexpr int kMaxMaskBlocks = 2048;  // 128-token blocks per sequence the mask builder accepts (256 Ki tokens)
 
 // Device address of the status word of the current device (NULL if the runtime refuses).
 int* device_status_word();

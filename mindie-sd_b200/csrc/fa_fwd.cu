@@ -375,57 +375,73 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     for (int i = 0; i < 32; ++i)
                         if (c * 32 + i >= tail_valid) s[c][i] = 0xff800000u;  // -inf
             }
-            float mx = -INFINITY;
+            // Eight independent chains: a single running max would be 128 dependent instructions.
+            float mx8[8];
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(__uint_as_float(s[0][i]), __uint_as_float(s[0][i + 8]));
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+            for (int i = 16; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(s[0][i]));
+#pragma unroll
+            for (int c = 1; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(s[c][i]));
+            const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                                   fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             const float m_cand = mx * mult;
             const bool need = m_cand > m_run + kLag;
-            if (__any_sync(0xffffffffu, need)) {
+            const bool rescale = __any_sync(0xffffffffu, need);
+            float alpha = 1.0f;
+            if (rescale) {
                 const float m_new = fmaxf(m_run, m_cand);
-                const float alpha = ex2_approx(m_run - m_new);  // 0 on the first block (m_run = -inf)
-                if (cnt > 0) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t o[32];
-                        tmem_ld32(taddr_o + c * 32, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(taddr_o + c * 32, o);
-                    }
-                }
+                alpha = ex2_approx(m_run - m_new);  // 0 on the first block (m_run = -inf)
                 l_run *= alpha;
                 m_run = m_new;
             }
             const float neg_m = kFp8 ? (kFp8PShiftLog2 + v_off - m_run) : -m_run;
-            float sum = 0.0f;
+            // x = s * mult - m as packed pairs (one instruction per two scores), then ex2 and pack.
+            const uint64_t mult2 = pack2(mult, mult), negm2 = pack2(neg_m, neg_m);
+            uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                if constexpr (kFp8) {
-                    uint32_t pk[8];
+                uint32_t pk[kFp8 ? 8 : 16];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float a = ex2_approx(fmaf(__uint_as_float(s[c][4 * i + 0]), mult, neg_m));
-                        const float b = ex2_approx(fmaf(__uint_as_float(s[c][4 * i + 1]), mult, neg_m));
-                        const float cc = ex2_approx(fmaf(__uint_as_float(s[c][4 * i + 2]), mult, neg_m));
-                        const float d = ex2_approx(fmaf(__uint_as_float(s[c][4 * i + 3]), mult, neg_m));
-                        sum += (a + b) + (cc + d);
-                        pk[i] = pack_quad_e4m3(a, b, cc, d);
+                for (int i = 0; i < 8; ++i) {
+                    float e0, e1, e2, e3;
+                    unpack2(fma2(pack2(__uint_as_float(s[c][4 * i]), __uint_as_float(s[c][4 * i + 1])), mult2, negm2), e0, e1);
+                    unpack2(fma2(pack2(__uint_as_float(s[c][4 * i + 2]), __uint_as_float(s[c][4 * i + 3])), mult2, negm2), e2, e3);
+                    e0 = ex2_approx(e0);
+                    e1 = ex2_approx(e1);
+                    e2 = ex2_approx(e2);
+                    e3 = ex2_approx(e3);
+                    sum2[0] = add2(sum2[0], pack2(e0, e1));
+                    sum2[1] = add2(sum2[1], pack2(e2, e3));
+                    if constexpr (kFp8) {
+                        pk[i] = pack_quad_e4m3(e0, e1, e2, e3);
+                    } else {
+                        pk[2 * i] = pack_pair(e0, e1, kIn);
+                        pk[2 * i + 1] = pack_pair(e2, e3, kIn);
                     }
-                    tmem_st8(taddr_s + c * 8, pk);
-                } else {
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float a = ex2_approx(fmaf(__uint_as_float(s[c][2 * i + 0]), mult, neg_m));
-                        const float b = ex2_approx(fmaf(__uint_as_float(s[c][2 * i + 1]), mult, neg_m));
-                        sum += a + b;
-                        pk[i] = pack_pair(a, b, kIn);
-                    }
-                    tmem_st16(taddr_s + c * 16, pk);
                 }
+                if constexpr (kFp8) tmem_st8(taddr_s + c * 8, pk);
+                else tmem_st16(taddr_s + c * 16, pk);
+            }
+            // The scores are dead now; the (rare) rescale of O reuses their registers.
+            if (rescale && cnt > 0) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(taddr_o + c * 32, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st32(taddr_o + c * 32, o);
+                }
+            }
+            float sum;
+            {
+                float a, b;
+                unpack2(add2(sum2[0], sum2[1]), a, b);
+                sum = a + b;
             }
             l_run += sum * l_fix;
             tmem_wait_st();

@@ -107,12 +107,18 @@ struct PoolParams {
     Grid g;
 };
 
+// Eight consecutive channels of one token: loaded raw (so that several loads can be in flight in
+// few registers) and widened to fp32 where they are consumed.
 template <typename T>
-__device__ __forceinline__ void load8(const T* ptr, float (&out)[8]);
+struct Raw8 {
+    uint4 v;
+    __device__ __forceinline__ void load(const T* ptr) { v = *reinterpret_cast<const uint4*>(ptr); }
+    __device__ __forceinline__ void zero() { v = make_uint4(0, 0, 0, 0); }
+    __device__ __forceinline__ void widen(float (&out)[8]) const;
+};
 template <>
-__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* ptr, float (&out)[8]) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(ptr);
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+__device__ __forceinline__ void Raw8<__nv_bfloat16>::widen(float (&out)[8]) const {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         out[2 * i] = __uint_as_float(w[i] << 16);
@@ -120,9 +126,8 @@ __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* ptr, f
     }
 }
 template <>
-__device__ __forceinline__ void load8<__half>(const __half* ptr, float (&out)[8]) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(ptr);
-    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+__device__ __forceinline__ void Raw8<__half>::widen(float (&out)[8]) const {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const float2 f = __half22float2(h[i]);
@@ -131,16 +136,23 @@ __device__ __forceinline__ void load8<__half>(const __half* ptr, float (&out)[8]
     }
 }
 template <>
-__device__ __forceinline__ void load8<float>(const float* ptr, float (&out)[8]) {
-    const float4 a = *reinterpret_cast<const float4*>(ptr);
-    const float4 b = *reinterpret_cast<const float4*>(ptr + 4);
-    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
-    out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
-}
+struct Raw8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* ptr) {
+        a = *reinterpret_cast<const float4*>(ptr);
+        b = *reinterpret_cast<const float4*>(ptr + 4);
+    }
+    __device__ __forceinline__ void zero() { a = b = make_float4(0, 0, 0, 0); }
+    __device__ __forceinline__ void widen(float (&out)[8]) const {
+        out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+        out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+    }
+};
 
 template <typename T>
 __global__ void __launch_bounds__(256) rf_pool_kernel(const PoolParams p, int ntensors) {
     extern __shared__ double red[];  // [row groups][dim]
+    __shared__ int src_tok[128];     // source token of each position of the block
     const int blk = blockIdx.x, head = blockIdx.y;
     const int which = ntensors == 2 ? (blockIdx.z & 1) : 0;
     const int batch = ntensors == 2 ? (blockIdx.z >> 1) : blockIdx.z;
@@ -156,23 +168,39 @@ __global__ void __launch_bounds__(256) rf_pool_kernel(const PoolParams p, int nt
         first = p.g.img + (blk - p.img_blocks) * 128;
         count = min(128, p.g.img + p.g.txt - first);
     }
-    const T* base = static_cast<const T*>(p.x[which]) + batch * p.stride[which][0] + head * p.stride[which][1];
+    // The permutation's index arithmetic (several integer divisions) once per row, not per lane.
+    if (threadIdx.x < count) src_tok[threadIdx.x] = source_of(p.g, first + threadIdx.x);
+    __syncthreads();
+    const T* base = static_cast<const T*>(p.x[which]) + batch * p.stride[which][0] + head * p.stride[which][1] + c * 8;
+    const int64_t tok_stride = p.stride[which][2];
     double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (grp < groups) {
-        for (int r = grp; r < count; r += groups) {
-            const int tok = source_of(p.g, first + r);
-            float vals[8];
-            load8<T>(base + tok * p.stride[which][2] + c * 8, vals);
+        // Eight rows per trip: the loads are issued back to back before any of them is consumed.
+        for (int r = grp; r < count; r += 8 * groups) {
+            Raw8<T> raw[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] += static_cast<double>(vals[i]);
+            for (int u = 0; u < 8; ++u) {
+                const int rr = r + u * groups;
+                if (rr < count) raw[u].load(base + src_tok[rr] * tok_stride);
+                else raw[u].zero();
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                float vals[8];
+                raw[u].widen(vals);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += static_cast<double>(vals[i]);
+            }
         }
+        // Channel c*8+i of row group grp goes to [grp][i][c]: consecutive lanes, consecutive slots.
 #pragma unroll
-        for (int i = 0; i < 8; ++i) red[grp * p.dim + c * 8 + i] = acc[i];
+        for (int i = 0; i < 8; ++i) red[grp * p.dim + i * lanes + c] = acc[i];
     }
     __syncthreads();
     for (int ch = threadIdx.x; ch < p.dim; ch += 256) {
         double s = 0;
-        for (int g2 = 0; g2 < groups; ++g2) s += red[g2 * p.dim + ch];
+        const int slot = (ch & 7) * lanes + (ch >> 3);
+        for (int g2 = 0; g2 < groups; ++g2) s += red[g2 * p.dim + slot];
         const int64_t o = ((static_cast<int64_t>(batch) * p.heads + head) * p.blocks + blk) * p.dim + ch;
         p.pooled[which][o] = static_cast<float>(s / static_cast<double>(count));
     }
@@ -186,7 +214,8 @@ __global__ void __launch_bounds__(256) rf_pool_kernel(const PoolParams p, int nt
 struct MaskParams {
     const float* q_pooled;  // [batch][heads][blocks][dim]
     const float* k_pooled;
-    int heads, dim, blocks, rows;
+    int heads, dim, blocks;
+    int vec_shift;  // log2(dim / 4)
     int keep_len;
     int txt_blocks, first_frame_blocks;
     int band;  // < 0: off
@@ -202,56 +231,104 @@ __device__ __forceinline__ unsigned long long order_key(double v) {
     return (b >> 63) ? ~b : (b | 0x8000000000000000ull);
 }
 
+constexpr int kMaskRows = 8;    // q blocks per CTA = M of the fp64 tensor-core tile
+constexpr int kMaskTile = 32;   // k blocks staged per trip
+
+__device__ __forceinline__ void dmma884(double& c0, double& c1, double a, double b) {
+    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};"
+                 : "+d"(c0), "+d"(c1)
+                 : "d"(a), "d"(b));
+}
+
+// kKeysPerLane: ceil(blocks / 32) rounded up to a supported size; the row's keys live in registers
+// during the threshold search.
+template <int kKeysPerLane>
 __global__ void __launch_bounds__(256) rf_mask_kernel(const MaskParams p) {
     extern __shared__ unsigned char smem_dyn[];
-    // layout: q rows [rows][dim] float | k tile [32][dim + 1] float | keys [rows][blocks] u64
-    float* sq = reinterpret_cast<float*>(smem_dyn);
-    float* sk = sq + p.rows * p.dim;
-    const int kpitch = p.dim + 1;
-    unsigned long long* keys =
-        reinterpret_cast<unsigned long long*>(smem_dyn + ((static_cast<size_t>(p.rows) * p.dim + 32 * kpitch) * 4 + 7) / 8 * 8);
+    // layout (8-byte units): q rows [8][dim + 4] | k tile [32][dim + 4] | partial sums [4][64] |
+    // keys [8][blocks].  q and k are widened to fp64 once when staged.  The pitch dim + 4 makes the
+    // tensor-core fragment loads (8 rows x 4 consecutive channels) hit 32 distinct 8-byte slots.
+    const int pitch = p.dim + 4;
+    double* sq = reinterpret_cast<double*>(smem_dyn);
+    double* sk = sq + kMaskRows * pitch;
+    double* part = sk + kMaskTile * pitch;
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(part + 4 * 64);
 
-    const int row0 = blockIdx.x * p.rows, head = blockIdx.y, batch = blockIdx.z;
-    const int nrows = min(p.rows, p.blocks - row0);
-    const int tid = threadIdx.x;
+    const int row0 = blockIdx.x * kMaskRows, head = blockIdx.y, batch = blockIdx.z;
+    const int nrows = min(kMaskRows, p.blocks - row0);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const float* qp = p.q_pooled + ((static_cast<int64_t>(batch) * p.heads + head) * p.blocks) * p.dim;
     const float* kp = p.k_pooled + ((static_cast<int64_t>(batch) * p.heads + head) * p.blocks) * p.dim;
 
-    for (int i = tid; i < nrows * p.dim; i += 256) sq[i] = qp[static_cast<int64_t>(row0) * p.dim + i];
+    // Staging: dim is a power of two; a thread moves 4 consecutive channels (one 16-byte load).
+    const int vec_per_row = p.dim >> 2, vshift = p.vec_shift;  // vec_per_row == 1 << vshift
+    auto stage = [&](double* dst, const float* src, int rows_total, int rows_valid) {
+        for (int i = tid; i < rows_total * vec_per_row; i += 256) {
+            const int r = i >> vshift, v = i & (vec_per_row - 1);
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < rows_valid) x = *reinterpret_cast<const float4*>(src + static_cast<int64_t>(r) * p.dim + v * 4);
+            double2* d = reinterpret_cast<double2*>(dst + r * pitch + v * 4);
+            d[0] = make_double2(static_cast<double>(x.x), static_cast<double>(x.y));
+            d[1] = make_double2(static_cast<double>(x.z), static_cast<double>(x.w));
+        }
+    };
+    stage(sq, qp + static_cast<int64_t>(row0) * p.dim, kMaskRows, nrows);
 
-    // Scores, 32 k-blocks at a time: thread (r, j) = (tid / 32, tid % 32) for rows r, r + 8, ...
-    for (int j0 = 0; j0 < p.blocks; j0 += 32) {
+    // Scores on the fp64 tensor cores: warp (cg, half) owns k columns 8cg..8cg+7 of the tile and one
+    // half of the channels; the two halves are added through shared memory.
+    const int cg = warp & 3, half = warp >> 2;
+    const int ch_begin = half * (p.dim >> 1), ch_end = ch_begin + (p.dim >> 1);
+    const int frag_row = lane >> 2, frag_k = lane & 3;
+    for (int j0 = 0; j0 < p.blocks; j0 += kMaskTile) {
         __syncthreads();
-        const int nj = min(32, p.blocks - j0);
-        for (int i = tid; i < nj * p.dim; i += 256) {
-            const int j = i / p.dim, ch = i - j * p.dim;
-            sk[j * kpitch + ch] = kp[static_cast<int64_t>(j0 + j) * p.dim + ch];
+        const int nj = min(kMaskTile, p.blocks - j0);
+        stage(sk, kp + static_cast<int64_t>(j0) * p.dim, kMaskTile, nj);
+        __syncthreads();
+        double c0 = 0.0, c1 = 0.0, d0 = 0.0, d1 = 0.0;  // two chains, so consecutive MMAs do not wait on each other
+        const double* a_ptr = sq + frag_row * pitch + frag_k;
+        const double* b_ptr = sk + (cg * 8 + frag_row) * pitch + frag_k;
+        int ch = ch_begin;
+        for (; ch + 8 <= ch_end; ch += 8) {
+            dmma884(c0, c1, a_ptr[ch], b_ptr[ch]);
+            dmma884(d0, d1, a_ptr[ch + 4], b_ptr[ch + 4]);
+        }
+        for (; ch < ch_end; ch += 4) dmma884(c0, c1, a_ptr[ch], b_ptr[ch]);
+        c0 += d0;
+        c1 += d1;
+        if (half == 1) {
+            part[cg * 64 + lane * 2] = c0;
+            part[cg * 64 + lane * 2 + 1] = c1;
         }
         __syncthreads();
-        const int j = tid & 31;
-        if (j < nj) {
-            for (int r = tid >> 5; r < nrows; r += 8) {
-                double acc = 0.0;
-                const float* a = sq + r * p.dim;
-                const float* b = sk + j * kpitch;
-                for (int ch = 0; ch < p.dim; ++ch) acc = fma(static_cast<double>(a[ch]), static_cast<double>(b[ch]), acc);
-                keys[static_cast<size_t>(r) * p.blocks + j0 + j] = order_key(acc);
+        if (half == 0) {
+            c0 += part[cg * 64 + lane * 2];
+            c1 += part[cg * 64 + lane * 2 + 1];
+            const int col = j0 + cg * 8 + frag_k * 2;
+            if (frag_row < nrows) {
+                if (col < p.blocks) keys[static_cast<size_t>(frag_row) * p.blocks + col] = order_key(c0);
+                if (col + 1 < p.blocks) keys[static_cast<size_t>(frag_row) * p.blocks + col + 1] = order_key(c1);
             }
         }
     }
     __syncthreads();
 
-    // One warp per row: bitwise search for the largest key value that at least keep_len keys reach.
-    const int warp = tid >> 5, lane = tid & 31;
+    // One warp per row.  Bitwise search for the largest key value that at least keep_len keys reach;
+    // a key of 0 (padding) never counts because every candidate is at least 1.
     for (int r = warp; r < nrows; r += 8) {
         const unsigned long long* kr = keys + static_cast<size_t>(r) * p.blocks;
+        unsigned long long mine[kKeysPerLane];
+#pragma unroll
+        for (int i = 0; i < kKeysPerLane; ++i) {
+            const int j = lane + 32 * i;
+            mine[i] = j < p.blocks ? kr[j] : 0ull;
+        }
         unsigned long long thr = 0;
         for (int bit = 63; bit >= 0; --bit) {
             const unsigned long long cand = thr | (1ull << bit);
             int cnt = 0;
-            for (int j = lane; j < p.blocks; j += 32) cnt += kr[j] >= cand;
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, d);
+            for (int i = 0; i < kKeysPerLane; ++i) cnt += mine[i] >= cand;
+            cnt = __reduce_add_sync(0xffffffffu, cnt);
             if (cnt >= p.keep_len) thr = cand;
         }
         const int qb = row0 + r;
@@ -268,11 +345,13 @@ __global__ void __launch_bounds__(256) rf_mask_kernel(const MaskParams p) {
                             ? p.select_idx + (static_cast<int64_t>(qb) * p.heads + head) * p.blocks
                             : nullptr;
         int kept = 0;
-        for (int j0 = 0; j0 < p.blocks; j0 += 32) {
-            const int j = j0 + lane;
+#pragma unroll
+        for (int i = 0; i < kKeysPerLane; ++i) {
+            const int j = lane + 32 * i;
+            if (32 * i >= p.blocks) break;  // warp-uniform
             bool keep = false;
             if (j < p.blocks) {
-                keep = row_forced || kr[j] >= thr || j >= p.blocks - p.txt_blocks || j < p.first_frame_blocks;
+                keep = row_forced || mine[i] >= thr || j >= p.blocks - p.txt_blocks || j < p.first_frame_blocks;
                 if (!keep && p.band >= 0 && q_img && j < p.img_blocks) {
                     const int k_lo = (j * 128) / p.g.hw;
                     const int k_hi = (min(j * 128 + 128, p.g.img) - 1) / p.g.hw;
@@ -291,10 +370,8 @@ __global__ void __launch_bounds__(256) rf_mask_kernel(const MaskParams p) {
     }
 }
 
-int mask_rows_per_cta(int blocks) { return blocks <= 1024 ? 8 : (blocks <= 2048 ? 4 : 2); }
-
-size_t mask_smem_bytes(int rows, int dim, int blocks) {
-    return ((static_cast<size_t>(rows) * dim + 32 * (dim + 1)) * 4 + 7) / 8 * 8 + static_cast<size_t>(rows) * blocks * 8;
+size_t mask_smem_bytes(int dim, int blocks) {
+    return (static_cast<size_t>(kMaskRows + kMaskTile) * (dim + 4) + 4 * 64 + static_cast<size_t>(kMaskRows) * blocks) * 8;
 }
 
 }  // namespace
@@ -410,7 +487,6 @@ int launch_mask(const float* q_pooled, const float* k_pooled, int batch, int hea
     mp.blocks = mp.img_blocks + mp.txt_blocks;
     if (mp.blocks < 1) return MINDIESD_E_SHAPE;
     if (mp.blocks > kMaxMaskBlocks) return MINDIESD_E_CAPACITY;
-    mp.rows = mask_rows_per_cta(mp.blocks);
     // Same double-precision expression as the reference's math.ceil(cols * (1 - sparsity)).
     mp.keep_len = static_cast<int>(ceil(static_cast<double>(mp.blocks) * (1.0 - sparsity)));
     if (mp.keep_len < 1) return MINDIESD_E_VALUE;
@@ -422,12 +498,24 @@ int launch_mask(const float* q_pooled, const float* k_pooled, int batch, int hea
     mp.mask = mask;
     mp.select_idx = select_idx;
     mp.select_num = select_num;
-    const size_t smem = mask_smem_bytes(mp.rows, mp.dim, mp.blocks);
-    cudaError_t e = cudaFuncSetAttribute(rf_mask_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    dim3 grid((mp.blocks + mp.rows - 1) / mp.rows, heads, batch);
-    rf_mask_kernel<<<grid, 256, smem, stream>>>(mp);
-    e = cudaGetLastError();
+    if (dim < 16 || dim > 512 || (dim & (dim - 1))) return MINDIESD_E_SHAPE;  // power of two
+    mp.vec_shift = 0;
+    while ((4 << mp.vec_shift) < dim) ++mp.vec_shift;
+    if (reinterpret_cast<uintptr_t>(q_pooled) % 16 || reinterpret_cast<uintptr_t>(k_pooled) % 16) return MINDIESD_E_STRIDE;
+    const size_t smem = mask_smem_bytes(mp.dim, mp.blocks);
+    dim3 grid((mp.blocks + kMaskRows - 1) / kMaskRows, heads, batch);
+    auto launch = [&](auto kernel) -> cudaError_t {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        kernel<<<grid, 256, smem, stream>>>(mp);
+        return cudaGetLastError();
+    };
+    const int per_lane = (mp.blocks + 31) / 32;
+    cudaError_t e;
+    if (per_lane <= 8) e = launch(rf_mask_kernel<8>);
+    else if (per_lane <= 20) e = launch(rf_mask_kernel<20>);
+    else if (per_lane <= 32) e = launch(rf_mask_kernel<32>);
+    else e = launch(rf_mask_kernel<64>);
     return e == cudaSuccess ? MINDIESD_OK : static_cast<int>(e);
 }
 
