@@ -206,7 +206,8 @@ def dense_or_ulysses(args, rank, world, device):
         out = torch.empty_like(q)
         step = lambda: _cabi.attention(q, k, v, head_first=False, out=out)  # noqa: E731
     else:
-        chunks = min(cfg.heads // world, 8)
+        from mindiesd.parallel import default_head_chunks
+        chunks = default_head_chunks(cfg.heads // world)
         launches_per_step = chunks
         step = lambda: ulysses_attention(q, k, v, head_chunks=chunks)  # noqa: E731
 

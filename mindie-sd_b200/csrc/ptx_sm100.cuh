@@ -55,7 +55,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 // ----------------------------------------------------------------------------------------------
-// TMA (tiled bulk tensor loads, no multicast)
+// TMA (tiled bulk tensor loads, each CTA fetching its own tiles)
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -1,3 +1,3 @@
-from .ulysses import ulysses_attention
+from .ulysses import ulysses_attention, default_head_chunks
 
-__all__ = ["ulysses_attention"]
+__all__ = ["ulysses_attention", "default_head_chunks"]

@@ -71,14 +71,19 @@ def _comm_stream(device):
     return _COMM_STREAMS[key]
 
 
+def default_head_chunks(local_heads: int, limit: int = 8) -> int:
+    """Largest divisor of the local head count that is at most `limit`."""
+    return max(d for d in range(1, min(local_heads, limit) + 1) if local_heads % d == 0)
+
+
 def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, group=None,
                       scale: Optional[float] = None, head_chunks: Optional[int] = None,
                       attn_fn: Optional[Callable] = None) -> torch.Tensor:
     """query/key/value: this rank's [B, S/P, N, D] slice (BSND).  Returns this rank's [B, S/P, N, D]
     slice of the attention output over the full sequence.
 
-    head_chunks: pieces the N/P local heads are cut into for overlap (default: one head per chunk,
-    at most 8 chunks).  attn_fn(q, k, v, scale) -> out on [B, S, h, D] BSND tensors replaces the local
+    head_chunks: pieces the N/P local heads are cut into for overlap (default: the largest divisor
+    of N/P that is at most 8).  attn_fn(q, k, v, scale) -> out on [B, S, h, D] BSND tensors replaces the local
     attention (sparse or FP8 variants); the default is the dense kernel.
     """
     if query.dim() != 4 or key.shape != query.shape or value.shape != query.shape:
@@ -95,7 +100,7 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
         return attn(query, key, value, scale)
     n_loc = n // world
     if head_chunks is None:
-        head_chunks = min(n_loc, 8)
+        head_chunks = default_head_chunks(n_loc)
     if head_chunks < 1 or n_loc % head_chunks:
         raise ParametersInvalid(f"head_chunks={head_chunks} must divide the {n_loc} local heads.")
     hc = n_loc // head_chunks
