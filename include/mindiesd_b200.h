@@ -256,6 +256,12 @@ int mindiesd_fa_block_quant(const mindiesd_quant_args* args, void* stream);
  */
 int mindiesd_device_status(void);
 
+/*
+ * The status word and its diagnostics without clearing them: out[0] code, out[1] number of the
+ * wait that gave up first, out[2..4] index of the thread block that reported it.  Synchronises.
+ */
+int mindiesd_device_status_detail(int32_t out[8]);
+
 int mindiesd_abi_version(void);
 
 #ifdef __cplusplus

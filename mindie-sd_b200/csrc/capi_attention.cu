@@ -7,7 +7,7 @@
 namespace sdb {
 
 namespace {
-__device__ int g_status_word;
+__device__ int g_status_word[8];  // [0] code, [1] wait site, [2..4] CTA index of the first report
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -78,14 +78,23 @@ extern "C" int mindiesd_device_status(void) {
     if (!w) return MINDIESD_E_DRIVER;
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return static_cast<int>(e);
-    int v = 0;
-    e = cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost);
+    int v[8] = {};
+    e = cudaMemcpy(v, w, sizeof(v), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return static_cast<int>(e);
-    if (v != 0) {
-        const int zero = 0;
-        cudaMemcpy(w, &zero, sizeof(int), cudaMemcpyHostToDevice);
+    if (v[0] != 0) {
+        const int zero[8] = {};
+        cudaMemcpy(w, zero, sizeof(zero), cudaMemcpyHostToDevice);
     }
-    return v;
+    return v[0];
+}
+
+extern "C" int mindiesd_device_status_detail(int32_t out[8]) {
+    int* w = device_status_word();
+    if (!w || !out) return MINDIESD_E_NULL;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaMemcpy(out, w, 8 * sizeof(int), cudaMemcpyDeviceToHost);
+    return e == cudaSuccess ? MINDIESD_OK : static_cast<int>(e);
 }
 
 extern "C" int mindiesd_attention_fwd(const mindiesd_attn_args* a, void* stream) {

@@ -34,6 +34,7 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units the running max may lag before O is rescaled
 constexpr float kFp8PShiftLog2 = 8.0f;     // e4m3 probabilities are stored as p * 2^8
+constexpr float kFp8Lag = 0.75f;           // 2^8.75 = 431 still fits e4m3 (max 448)
 
 template <bool kFp8>
 struct Cfg {
@@ -104,6 +105,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     static_assert(kNumBars * 8 + 16 <= 256, "barrier area");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* abort_site = abort_flag + 1;  // which wait gave up first (diagnostics)
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -115,6 +117,10 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     const int q_row0 = qpair * 2 * kTile;
     const bool tile1_valid = q_row0 + kTile < p.seq_q;
     const int nkb = p.kv_blocks;
+
+    // A grid in which one CTA already gave up a wait is not going to produce a usable result: the
+    // remaining CTAs leave at once instead of each running into its own time-out.
+    if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
 
     // ---- set-up -------------------------------------------------------------------------------
     if (tid == 0) {
@@ -128,6 +134,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             mbar_init(bar_p(t), kTile);
         }
         *abort_flag = 0;
+        *abort_site = 0;
         fence_mbar_init();
     }
     if (warp == kLoadWarp && lane == 0) {
@@ -203,7 +210,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             bool ok = true;
             for (int u = next_block(0); u >= 0 && ok; u = next_block(u + 1)) {
                 for (int which = 0; which < 2 && ok; ++which) {  // 0: K block, 1: V block
-                    ok = mbar_wait(bar_empty(ring.idx), ring.phase ^ 1u, abort_flag);
+                    ok = mbar_wait(bar_empty(ring.idx), ring.phase ^ 1u, abort_flag, 1);
                     if (!ok) break;
                     mbar_arrive_expect_tx(bar_full(ring.idx), C::kTileBytes);
                     const CUtensorMap* tm = which ? &p.tm_v : &p.tm_k;
@@ -215,11 +222,11 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 }
             }
             // Before the CTA may exit, every copy this thread started must have landed.
-            mbar_wait(bar_q(), 0, abort_flag);
+            mbar_wait(bar_q(), 0, abort_flag, 2);
             const int pending = issued < C::kStages ? issued : C::kStages;
             for (int i = 0; i < pending; ++i) {
                 const int n = issued - 1 - i;  // n-th load overall
-                mbar_wait(bar_full(n % C::kStages), static_cast<uint32_t>(n / C::kStages) & 1u, abort_flag);
+                mbar_wait(bar_full(n % C::kStages), static_cast<uint32_t>(n / C::kStages) & 1u, abort_flag, 3);
             }
         }
     } else if (warp == kMmaWarp) {
@@ -253,12 +260,12 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 }
             };
 
-            bool ok = mbar_wait(bar_q(), 0, abort_flag);
+            bool ok = mbar_wait(bar_q(), 0, abort_flag, 10);
             Ring ring;
             int pv_cnt[2] = {0, 0};
             int u = next_block(0);
             if (ok && u >= 0) {
-                ok = mbar_wait(bar_full(ring.idx), ring.phase, abort_flag);
+                ok = mbar_wait(bar_full(ring.idx), ring.phase, abort_flag, 11);
                 if (ok) {
                     tc_fence_after();
                     const int f = flags_of(u);
@@ -277,23 +284,23 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 const Ring kslot = ring;
                 if (nf) ring.template next<C::kStages>();
 
-                ok = mbar_wait(bar_full(vslot.idx), vslot.phase, abort_flag);
+                ok = mbar_wait(bar_full(vslot.idx), vslot.phase, abort_flag, 12);
                 if (!ok) break;
                 if (f & 1) {
-                    ok = mbar_wait(bar_p(0), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag);
+                    ok = mbar_wait(bar_p(0), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13);
                     if (!ok) break;
                     tc_fence_after();
                     issue_pv(0, vslot.idx, pv_cnt[0] > 0);
                     ++pv_cnt[0];
                 }
                 if (nf) {
-                    ok = mbar_wait(bar_full(kslot.idx), kslot.phase, abort_flag);
+                    ok = mbar_wait(bar_full(kslot.idx), kslot.phase, abort_flag, 17);
                     if (!ok) break;
                     tc_fence_after();
                 }
                 if (nf & 1) issue_s(0, kslot.idx);
                 if (f & 2) {
-                    ok = mbar_wait(bar_p(1), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag);
+                    ok = mbar_wait(bar_p(1), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14);
                     if (!ok) break;
                     tc_fence_after();
                     issue_pv(1, vslot.idx, pv_cnt[1] > 0);
@@ -320,7 +327,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         const int tail_valid = p.seq_kv - (nkb - 1) * kTile;  // valid columns of the last kv block
         // The running max may lag the true max by this much (log2 units) before O is rescaled; the
         // probabilities then reach 2^lag, which two-byte formats hold but e4m3 does not.
-        constexpr float kLag = kFp8 ? 0.0f : kRescaleThreshold;
+        constexpr float kLag = kFp8 ? kFp8Lag : kRescaleThreshold;
 
         // e4m3: the dequantisation scales of the q block and of each k block fold into the
         // exponent's multiplier; a per-token-block v scale folds into the exponent's offset.
@@ -348,7 +355,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         bool ok = true;
         for (int j = 0; j < nkb; ++j) {
             if (!my_flags[j]) continue;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_s(t), static_cast<uint32_t>(cnt) & 1u, abort_flag));
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_s(t), static_cast<uint32_t>(cnt) & 1u, abort_flag, 20 + t));
             if (!ok) break;
             tc_fence_after();
 
@@ -367,81 +374,91 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     l_fix = 1.0f / r;
                 }
             }
-
-            if (j == nkb - 1 && tail_valid < kTile) {
+            const bool tail = j == nkb - 1 && tail_valid < kTile;
+            if (tail) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
                         if (c * 32 + i >= tail_valid) s[c][i] = 0xff800000u;  // -inf
             }
-            // Eight independent chains: a single running max would be 128 dependent instructions.
-            float mx8[8];
+            auto row_max = [&]() {
+                // Eight independent chains: a single running max would be 128 dependent instructions.
+                float mx8[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(__uint_as_float(s[0][i]), __uint_as_float(s[0][i + 8]));
+                for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(__uint_as_float(s[0][i]), __uint_as_float(s[0][i + 8]));
 #pragma unroll
-            for (int i = 16; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(s[0][i]));
+                for (int i = 16; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(s[0][i]));
 #pragma unroll
-            for (int c = 1; c < 4; ++c)
+                for (int c = 1; c < 4; ++c)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(s[c][i]));
-            const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                                   fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-            const float m_cand = mx * mult;
-            const bool need = m_cand > m_run + kLag;
-            const bool rescale = __any_sync(0xffffffffu, need);
-            float alpha = 1.0f;
-            if (rescale) {
+                    for (int i = 0; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(s[c][i]));
+                return fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+            };
+            // The probabilities are computed against the running max right away; the block's own max
+            // is found alongside (it does not touch the exponent unit) and only if it exceeds the
+            // running max by more than the allowed lag -- rare after the first blocks -- is the block
+            // redone.  This keeps the max off the critical path.  The first block has no running max
+            // yet and takes its own first.
+            float alpha_total = 1.0f;
+            if (cnt == 0) m_run = row_max() * mult;
+            const uint64_t mult2 = pack2(mult, mult);
+            float sum = 0.0f;
+#pragma unroll 1
+            for (int pass = 0; pass < 2; ++pass) {
+                const float neg_m = kFp8 ? (kFp8PShiftLog2 + v_off - m_run) : -m_run;
+                const uint64_t negm2 = pack2(neg_m, neg_m);
+                uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t pk[kFp8 ? 8 : 16];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float e0, e1, e2, e3;
+                        unpack2(fma2(pack2(__uint_as_float(s[c][4 * i]), __uint_as_float(s[c][4 * i + 1])), mult2, negm2), e0, e1);
+                        e0 = ex2_approx(e0);
+                        e1 = ex2_approx(e1);
+                        unpack2(fma2(pack2(__uint_as_float(s[c][4 * i + 2]), __uint_as_float(s[c][4 * i + 3])), mult2, negm2), e2, e3);
+                        e2 = ex2_approx(e2);
+                        e3 = ex2_approx(e3);
+                        sum2[0] = add2(sum2[0], pack2(e0, e1));
+                        sum2[1] = add2(sum2[1], pack2(e2, e3));
+                        if constexpr (kFp8) {
+                            pk[i] = pack_quad_e4m3(e0, e1, e2, e3);
+                        } else {
+                            pk[2 * i] = pack_pair(e0, e1, kIn);
+                            pk[2 * i + 1] = pack_pair(e2, e3, kIn);
+                        }
+                    }
+                    if constexpr (kFp8) tmem_st8(taddr_s + c * 8, pk);
+                    else tmem_st16(taddr_s + c * 16, pk);
+                }
+                {
+                    float a, b;
+                    unpack2(add2(sum2[0], sum2[1]), a, b);
+                    sum = a + b;
+                }
+                if (pass == 1 || cnt == 0) break;
+                const float m_cand = row_max() * mult;
+                if (!__any_sync(0xffffffffu, m_cand > m_run + kLag)) break;
                 const float m_new = fmaxf(m_run, m_cand);
-                alpha = ex2_approx(m_run - m_new);  // 0 on the first block (m_run = -inf)
-                l_run *= alpha;
+                alpha_total = ex2_approx(m_run - m_new);
                 m_run = m_new;
             }
-            const float neg_m = kFp8 ? (kFp8PShiftLog2 + v_off - m_run) : -m_run;
-            // x = s * mult - m as packed pairs (one instruction per two scores), then ex2 and pack.
-            const uint64_t mult2 = pack2(mult, mult), negm2 = pack2(neg_m, neg_m);
-            uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t pk[kFp8 ? 8 : 16];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    float e0, e1, e2, e3;
-                    unpack2(fma2(pack2(__uint_as_float(s[c][4 * i]), __uint_as_float(s[c][4 * i + 1])), mult2, negm2), e0, e1);
-                    unpack2(fma2(pack2(__uint_as_float(s[c][4 * i + 2]), __uint_as_float(s[c][4 * i + 3])), mult2, negm2), e2, e3);
-                    e0 = ex2_approx(e0);
-                    e1 = ex2_approx(e1);
-                    e2 = ex2_approx(e2);
-                    e3 = ex2_approx(e3);
-                    sum2[0] = add2(sum2[0], pack2(e0, e1));
-                    sum2[1] = add2(sum2[1], pack2(e2, e3));
-                    if constexpr (kFp8) {
-                        pk[i] = pack_quad_e4m3(e0, e1, e2, e3);
-                    } else {
-                        pk[2 * i] = pack_pair(e0, e1, kIn);
-                        pk[2 * i + 1] = pack_pair(e2, e3, kIn);
-                    }
-                }
-                if constexpr (kFp8) tmem_st8(taddr_s + c * 8, pk);
-                else tmem_st16(taddr_s + c * 16, pk);
-            }
+            const bool rescale = alpha_total != 1.0f;  // per thread; the warp-wide decision follows
+            l_run *= alpha_total;
             // The scores are dead now; the (rare) rescale of O reuses their registers.
-            if (rescale && cnt > 0) {
+            if (cnt > 0 && __any_sync(0xffffffffu, rescale)) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t o[32];
                     tmem_ld32(taddr_o + c * 32, o);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha_total);
                     tmem_st32(taddr_o + c * 32, o);
                 }
-            }
-            float sum;
-            {
-                float a, b;
-                unpack2(add2(sum2[0], sum2[1]), a, b);
-                sum = a + b;
             }
             l_run += sum * l_fix;
             tmem_wait_st();
@@ -449,7 +466,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             mbar_arrive(bar_p(t));
             ++cnt;
         }
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_s(t), static_cast<uint32_t>(cnt) & 1u, abort_flag));
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_s(t), static_cast<uint32_t>(cnt) & 1u, abort_flag, 26 + t));
         if (ok && (t == 0 || tile1_valid)) {  // warp-uniform: the tensor-memory loads are warp-collective
             tc_fence_after();
             const bool row_ok = q_row < p.seq_q;
@@ -514,7 +531,15 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
-    if (tid == 0 && *abort_flag && p.status) atomicCAS(p.status, 0, kStatusFaWaitGaveUp);
+    if (tid == 0 && *abort_flag && p.status) {
+        // First CTA to report wins the word and leaves where it stopped behind it.
+        if (atomicCAS(p.status, 0, kStatusFaWaitGaveUp) == 0) {
+            p.status[1] = *abort_site;
+            p.status[2] = static_cast<int>(blockIdx.x);
+            p.status[3] = static_cast<int>(blockIdx.y);
+            p.status[4] = static_cast<int>(blockIdx.z);
+        }
+    }
 }
 
 int fa_fwd_smem_bytes(bool fp8) { return (fp8 ? Cfg<true>::kSmemBytes : Cfg<false>::kSmemBytes) + 1024; }

@@ -39,17 +39,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Spin limit of a bounded wait. try_wait itself suspends the thread for a hardware-chosen
-// interval, so this many attempts is of the order of seconds: far beyond any legitimate wait.
-constexpr uint32_t kSpinLimit = 1u << 24;
+// Spin limit of a bounded wait.  try_wait itself suspends the thread for a hardware-chosen
+// interval (of the order of a microsecond), so this many attempts is tens of milliseconds to a
+// second: far beyond any legitimate wait inside a kernel, short enough that a grid of stuck
+// CTAs still drains in seconds.
+constexpr uint32_t kSpinLimit = 1u << 18;
 
-// Waits for the phase with the given parity. Returns false if the wait gave up (limit reached
-// or another role of the CTA raised the abort flag); the first to give up raises the flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// Waits for the phase with the given parity.  Returns false if the wait gave up (limit reached
+// or another role of the CTA raised the abort flag); the first to give up raises the flag and
+// leaves `site` (a small number naming the wait) next to it.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site = 0) {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 255u && *abort_flag) return false;
     }
+    if (*abort_flag == 0) abort_flag[1] = site;
     *abort_flag = 1;
     return false;
 }
