@@ -238,25 +238,26 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             const uint32_t col_s[2] = {tmem_base + kColS0, tmem_base + kColS1};
             const uint32_t col_o[2] = {tmem_base + kColO0, tmem_base + kColO1};
 
+            const uint32_t q_lo[2] = {desc_lo(smem_u32(sm_q), 16), desc_lo(smem_u32(sm_q + C::kTileBytes), 16)};
+            const uint32_t ring_k_lo = desc_lo(smem_u32(sm_ring), 16);
+            const uint32_t ring_v_lo = desc_lo(smem_u32(sm_ring), C::kAtomBytes);
+            constexpr uint32_t kSlotStep = C::kTileBytes >> 4;
             auto issue_s = [&](int t, int slot) {
-                const uint32_t qa = smem_u32(sm_q + t * C::kTileBytes);
-                const uint32_t ka = smem_u32(sm_ring + slot * C::kTileBytes);
+                const uint32_t k_lo = ring_k_lo + slot * kSlotStep;
 #pragma unroll
                 for (int kc = 0; kc < C::kQkSteps; ++kc) {
-                    const uint32_t off = (kc >> 2) * C::kAtomBytes + (kc & 3) * 32;
-                    umma_ss<kFp8>(col_s[t], smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024),
-                                  idesc_qk, kc > 0);
+                    constexpr uint32_t kAtom16 = C::kAtomBytes >> 4;
+                    const uint32_t off = (kc >> 2) * kAtom16 + (kc & 3) * 2;
+                    umma_ss_lohi<kFp8>(col_s[t], q_lo[t] + off, k_lo + off, kDescHiSbo1024, idesc_qk, kc > 0);
                 }
                 umma_commit(bar_s(t));
             };
             auto issue_pv = [&](int t, int slot, bool accumulate) {
-                const uint32_t va = smem_u32(sm_ring + slot * C::kTileBytes);
+                const uint32_t v_lo = ring_v_lo + slot * kSlotStep;
 #pragma unroll
                 for (int kc = 0; kc < C::kPvSteps; ++kc) {
-                    // A: 8 tensor-memory columns per step (16 two-byte or 32 one-byte probabilities).
-                    umma_ts<kFp8>(col_o[t], col_s[t] + kc * 8,
-                                  smem_desc_sw128(va + kc * C::kPvK * 128, C::kAtomBytes, 1024), idesc_pv,
-                                  (accumulate || kc > 0) ? 1u : 0u);
+                    umma_ts_lohi<kFp8>(col_o[t], col_s[t] + kc * 8, v_lo + kc * (C::kPvK * 128 >> 4), kDescHiSbo1024, idesc_pv,
+                                       (accumulate || kc > 0) ? 1u : 0u);
                 }
             };
 
@@ -402,7 +403,18 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             // redone.  This keeps the max off the critical path.  The first block has no running max
             // yet and takes its own first.
             float alpha_total = 1.0f;
-            if (cnt == 0) m_run = row_max() * mult;
+            if (cnt == 0) {
+                m_run = row_max() * mult;
+            } else if (kFp8) {
+                // e4m3 leaves less than one binade of lag, so a speculative pass would be redone too
+                // often: take the block max first.
+                const float m_cand = row_max() * mult;
+                if (__any_sync(0xffffffffu, m_cand > m_run + kLag)) {
+                    const float m_new = fmaxf(m_run, m_cand);
+                    alpha_total = ex2_approx(m_run - m_new);
+                    m_run = m_new;
+                }
+            }
             const uint64_t mult2 = pack2(mult, mult);
             float sum = 0.0f;
 #pragma unroll 1
@@ -439,7 +451,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     unpack2(add2(sum2[0], sum2[1]), a, b);
                     sum = a + b;
                 }
-                if (pass == 1 || cnt == 0) break;
+                if (pass == 1 || cnt == 0 || kFp8) break;
                 const float m_cand = row_max() * mult;
                 if (!__any_sync(0xffffffffu, m_cand > m_run + kLag)) break;
                 const float m_new = fmaxf(m_run, m_cand);

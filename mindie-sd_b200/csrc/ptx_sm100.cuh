@@ -145,60 +145,64 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8])
 // ----------------------------------------------------------------------------------------------
 // tcgen05.mma (one CTA, issued by a single thread) and its completion signal
 // ----------------------------------------------------------------------------------------------
-// D[tmem] (+)= A[smem] * B[smem]
+// D[tmem] (+)= A * B with A from shared memory (ss) or tensor memory (ts) and B from shared memory.
+// Descriptors are given as (low word, high word) pairs.  The thread that
+// issues the MMAs runs alone, so every scalar instruction between two MMAs is exposed latency:
+// callers keep the high word constant and derive the low word (start address field) with one add.
 template <bool kFp8>
-__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                        uint32_t accumulate) {
+__device__ __forceinline__ void umma_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                             uint32_t idesc, uint32_t accumulate) {
     if constexpr (kFp8) {
         asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\tsetp.ne.b32 p, %5, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
             : "memory");
     } else {
         asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\tsetp.ne.b32 p, %5, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
             : "memory");
     }
 }
-// D[tmem] (+)= A[tmem] * B[smem]
 template <bool kFp8>
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
-                                        uint32_t accumulate) {
+__device__ __forceinline__ void umma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi,
+                                             uint32_t idesc, uint32_t accumulate) {
     if constexpr (kFp8) {
         asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+            "mov.b64 db, {%2, %3};\n\tsetp.ne.b32 p, %5, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], db, %4, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
             : "memory");
     } else {
         asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-            ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+            "mov.b64 db, {%2, %3};\n\tsetp.ne.b32 p, %5, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
             : "memory");
     }
 }
+// Shared-memory matrix descriptor of a 128-byte-swizzled operand tile, as low and high word.
+//   bits  0..13  start address >> 4        bits 16..29  leading byte offset >> 4
+//   bits 32..45  stride byte offset >> 4   bit 46 descriptor version   bits 61..63  2 = 128-byte swizzle
+//   K-major  (rows of 128 B along the contraction dim): lbo unused (16), sbo = bytes between 8-row groups.
+//   MN-major (rows of 128 B along the M/N dim): lbo = bytes between 128-B column groups,
+//                                               sbo = bytes between 8-row (K) groups.
+// sbo is 1024 for every operand tile of these kernels, so one high word serves them all.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+    return ((addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+constexpr uint32_t kDescHiSbo1024 = (1024u >> 4) | (1u << 14) | (2u << 29);
+
 // The mbarrier receives one arrival once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
-}
-
-// Shared-memory matrix descriptor for a 128-byte-swizzled operand tile.
-//   K-major  (rows of 128 B along the contraction dim): sbo = bytes between 8-row groups.
-//   MN-major (rows of 128 B along the M/N dim):         lbo = bytes between 128-B column groups,
-//                                                       sbo = bytes between 8-row (K) groups.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
-    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    d |= 1ull << 46;  // descriptor version of this architecture
-    d |= 2ull << 61;  // 128-byte swizzle
-    return d;
 }
 
 // Instruction descriptor: fp32 accumulate, A and B of one operand format, M x N tile.
