@@ -217,16 +217,23 @@ def dense_or_ulysses(args, rank, world, device):
     clocks = sampler.stop()
 
     # End to end through the public Python API with host buffers: every step copies this rank's
-    # q, k, v from pinned host memory and reads its output back.
-    hq, hk, hv = (torch.empty(x.shape, dtype=x.dtype, pin_memory=True).copy_(x) for x in (q, k, v))
-    ho = torch.empty(q.shape, dtype=q.dtype, pin_memory=True)
+    # q, k, v from pinned host memory and reads its output back.  On one GPU the public
+    # attention_forward_host pipelines the copies with the kernel, head chunk by head chunk.
+    if world == 1:
+        hq, hk, hv = (torch.empty(x.transpose(1, 2).shape, dtype=x.dtype, pin_memory=True).copy_(x.transpose(1, 2))
+                      for x in (q, k, v))  # head-first pinned copies
+    else:
+        hq, hk, hv = (torch.empty(x.shape, dtype=x.dtype, pin_memory=True).copy_(x) for x in (q, k, v))
+    ho = torch.empty(hq.shape, dtype=q.dtype, pin_memory=True)
+    from mindiesd import attention_forward_host
+    e2e_chunks = 5 if cfg.heads % 5 == 0 else 1
 
     def e2e_step():
-        dq, dk, dv = (h.to(device, non_blocking=True) for h in (hq, hk, hv))
         if world == 1:
-            o = attention_forward(dq, dk, dv, head_first=False)
-        else:
-            o = ulysses_attention(dq, dk, dv, head_chunks=launches_per_step)
+            attention_forward_host(hq, hk, hv, out=ho, head_chunks=e2e_chunks)
+            return
+        dq, dk, dv = (h.to(device, non_blocking=True) for h in (hq, hk, hv))
+        o = ulysses_attention(dq, dk, dv, head_chunks=launches_per_step)
         ho.copy_(o, non_blocking=True)
 
     e2e_steps = max(1, min(args.steps, 5))
@@ -255,7 +262,8 @@ def dense_or_ulysses(args, rank, world, device):
                 "h2d_bytes_per_step": 3 * q.numel() * q.element_size() * world,
                 "d2h_bytes_per_step": q.numel() * q.element_size() * world,
                 "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
-                "api": "mindiesd.attention_forward" if world == 1 else "mindiesd.ulysses_attention"},
+                "api": f"mindiesd.attention_forward_host ({e2e_chunks} head chunks, copies overlapped)" if world == 1
+                       else "mindiesd.ulysses_attention"},
         "gpu_launches": launches_per_step * args.steps,
     }
     if world == 1:

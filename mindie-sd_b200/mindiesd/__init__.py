@@ -1,8 +1,9 @@
 """B200-native attention hot path behind the MindIE-SD layer API."""
-from .layers import attention_forward, sparse_attention
+from .cache_agent import CacheAgent, CacheConfig
+from .layers import attention_forward, attention_forward_varlen, attention_forward_host, sparse_attention
 from .parallel import ulysses_attention
 from .quantization import FP8RotateQuantFA
 from .utils import ParametersInvalid, ConfigError, ModelInitError, ModelExecError
 
-__all__ = ["attention_forward", "sparse_attention", "ulysses_attention", "FP8RotateQuantFA",
+__all__ = ["CacheAgent", "CacheConfig", "attention_forward", "attention_forward_varlen", "attention_forward_host", "sparse_attention", "ulysses_attention", "FP8RotateQuantFA",
            "ParametersInvalid", "ConfigError", "ModelInitError", "ModelExecError"]

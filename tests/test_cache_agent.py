@@ -1,0 +1,64 @@
+"""Host logic of the attention cache and the block-mask cache (CPU only): which (step, block) calls
+compute and which reuse, following the schedule of MindIE-SD's AttentionCache
+(mindiesd/cache_agent/attention_cache.py:22-31)."""
+import pytest
+
+from mindiesd import CacheAgent, CacheConfig, ConfigError, ParametersInvalid
+
+
+def _expected_reuse(step, start, interval, end):
+    return start < step <= end and (step - start) % interval != 0
+
+
+@pytest.mark.parametrize("start,interval,end", [(0, 2, 10000), (2, 3, 8), (1, 4, 5)])
+def test_attention_cache_schedule(start, interval, end):
+    blocks, steps = 3, 10
+    agent = CacheAgent(CacheConfig("attention_cache", blocks, steps, step_start=start, step_interval=interval, step_end=end))
+    for run in range(2):  # the counters wrap after steps_count steps and the cache is dropped
+        calls = []
+        for step in range(steps):
+            for block in range(blocks):
+                out = agent.apply(lambda s=step, b=block: calls.append((s, b)) or (s, b))
+                if _expected_reuse(step, start, interval, end):
+                    last = max(s for s in range(step) if not _expected_reuse(s, start, interval, end))
+                    assert out == (last, block)
+                else:
+                    assert out == (step, block)
+        assert calls == [(s, b) for s in range(steps) for b in range(blocks) if not _expected_reuse(s, start, interval, end)]
+
+
+def test_cache_agent_pass_through_and_errors():
+    n = []
+    agent = CacheAgent(CacheConfig("attention_cache", 2, 4, step_interval=1))
+    for _ in range(8):
+        agent.apply(lambda: n.append(1))
+    assert len(n) == 8
+    with pytest.raises(ParametersInvalid):
+        agent.apply(3)
+    with pytest.raises(ConfigError):
+        CacheAgent(CacheConfig("nope", 2, 4))
+    with pytest.raises(ConfigError):
+        CacheAgent(CacheConfig("dit_block_cache", 2, 4))
+    with pytest.raises(ConfigError):
+        CacheAgent(CacheConfig("attention_cache", 0, 4))
+    with pytest.raises(ConfigError):
+        CacheAgent(CacheConfig("attention_cache", 2, 4, step_start=5, step_end=3))
+
+
+def test_block_mask_cache_hands_the_kept_mask_back():
+    blocks, steps = 2, 6
+    agent = CacheAgent(CacheConfig("block_mask_cache", blocks, steps, step_start=0, step_interval=3))
+    seen = []
+
+    def attention(tag, cached_mask=None):
+        seen.append((tag, cached_mask))
+        return f"out{tag}", cached_mask if cached_mask is not None else f"mask{tag}"
+
+    for step in range(steps):
+        for block in range(blocks):
+            assert agent.apply(attention, (step, block)) == f"out{(step, block)}"
+    for (step, block), cached in seen:
+        if step % 3 == 0:
+            assert cached is None  # the builder runs
+        else:
+            assert cached == f"mask{(step - step % 3, block)}"

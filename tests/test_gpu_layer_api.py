@@ -178,3 +178,38 @@ def test_ops_trace_with_fake_tensors():
         assert out.shape == q.shape and lse.shape == (1, 2, 1024, 1)
         lse, out = torch.ops.mindiesd.la(q, q, q)
         assert out.dtype == torch.float32
+
+
+def test_attention_forward_host_pipeline():
+    from mindiesd import attention_forward_host, ParametersInvalid
+    q, k, v = (inputs.randn(210 + i, 1, 6, 700, 128, dtype=torch.bfloat16).pin_memory() for i in range(3))
+    want = oa.attention_math(q, k, v, head_first=True)
+    for chunks in (1, 3):
+        out = attention_forward_host(q, k, v, head_chunks=chunks)
+        assert out.is_pinned() and not out.is_cuda
+        _close(out, want)
+    with pytest.raises(ParametersInvalid):
+        attention_forward_host(q, k, v, head_chunks=4)
+    with pytest.raises(ParametersInvalid):
+        attention_forward_host(q.cuda(), k, v)
+
+
+def test_attention_forward_varlen():
+    from mindiesd import attention_forward_varlen, ParametersInvalid
+    lens_q, lens_k = [300, 1, 515], [300, 77, 640]
+    q = inputs.randn(220, sum(lens_q), 2, 128, dtype=torch.bfloat16)
+    k, v = (inputs.randn(221 + i, sum(lens_k), 2, 128, dtype=torch.bfloat16) for i in range(2))
+    cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32)
+    out = attention_forward_varlen(q.cuda(), k.cuda(), v.cuda(), cu_q, cu_k)
+    assert out.shape == q.shape
+    for i in range(3):
+        qs, ks = slice(int(cu_q[i]), int(cu_q[i + 1])), slice(int(cu_k[i]), int(cu_k[i + 1]))
+        want = oa.attention_math(q[qs][None], k[ks][None], v[ks][None], head_first=False)[0]
+        _close(out[qs], want)
+    with pytest.raises(ParametersInvalid):
+        attention_forward_varlen(q.cuda(), k.cuda(), v.cuda(), cu_q, cu_k, max_seqlen_q=515)
+    with pytest.raises(ParametersInvalid):
+        attention_forward_varlen(q.cuda(), k.cuda(), v.cuda(), cu_q, cu_k, dropout_p=0.1)
+    with pytest.raises(ParametersInvalid):
+        attention_forward_varlen(q.cuda()[None], k.cuda(), v.cuda(), cu_q, cu_k)
