@@ -100,8 +100,11 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     auto bar_full = [&](int s) { return bar_base + 8u * (1 + s); };
     auto bar_empty = [&](int s) { return bar_base + 8u * (1 + C::kStages + s); };
     auto bar_s = [&](int t) { return bar_base + 8u * (1 + 2 * C::kStages + t); };
-    auto bar_p = [&](int t) { return bar_base + 8u * (3 + 2 * C::kStages + t); };
-    constexpr int kNumBars = 5 + 2 * C::kStages;
+    // e4m3: probabilities are handed over in two halves (keys 0-63, 64-127) so that the first half of
+    // the P V product runs while the second half of the exponentials is still being taken.  Two-byte
+    // operands hand a block over whole, on the second barrier.
+    auto bar_p = [&](int t, int h) { return bar_base + 8u * (3 + 2 * C::kStages + 2 * t + h); };
+    constexpr int kNumBars = 7 + 2 * C::kStages;
     static_assert(kNumBars * 8 + 16 <= 256, "barrier area");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -131,7 +134,8 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar_s(t), 1);
-            mbar_init(bar_p(t), kTile);
+            mbar_init(bar_p(t, 0), kTile);
+            mbar_init(bar_p(t, 1), kTile);
         }
         *abort_flag = 0;
         *abort_site = 0;
@@ -252,10 +256,11 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 }
                 umma_commit(bar_s(t));
             };
-            auto issue_pv = [&](int t, int slot, bool accumulate) {
+            auto issue_pv = [&](int t, int h, int slot, bool accumulate) {  // keys 64h .. 64h+63 of the block
                 const uint32_t v_lo = ring_v_lo + slot * kSlotStep;
 #pragma unroll
-                for (int kc = 0; kc < C::kPvSteps; ++kc) {
+                for (int kk = 0; kk < C::kPvSteps / 2; ++kk) {
+                    const int kc = h * (C::kPvSteps / 2) + kk;
                     umma_ts_lohi<kFp8>(col_o[t], col_s[t] + kc * 8, v_lo + kc * (C::kPvK * 128 >> 4), kDescHiSbo1024, idesc_pv,
                                        (accumulate || kc > 0) ? 1u : 0u);
                 }
@@ -288,10 +293,17 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 ok = mbar_wait(bar_full(vslot.idx), vslot.phase, abort_flag, 12);
                 if (!ok) break;
                 if (f & 1) {
-                    ok = mbar_wait(bar_p(0), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13);
+                    if constexpr (kFp8) {
+                        ok = mbar_wait(bar_p(0, 0), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_pv(0, 0, vslot.idx, pv_cnt[0] > 0);
+                    }
+                    ok = mbar_wait(bar_p(0, 1), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_pv(0, vslot.idx, pv_cnt[0] > 0);
+                    if constexpr (!kFp8) issue_pv(0, 0, vslot.idx, pv_cnt[0] > 0);
+                    issue_pv(0, 1, vslot.idx, true);
                     ++pv_cnt[0];
                 }
                 if (nf) {
@@ -301,10 +313,17 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 }
                 if (nf & 1) issue_s(0, kslot.idx);
                 if (f & 2) {
-                    ok = mbar_wait(bar_p(1), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14);
+                    if constexpr (kFp8) {
+                        ok = mbar_wait(bar_p(1, 0), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_pv(1, 0, vslot.idx, pv_cnt[1] > 0);
+                    }
+                    ok = mbar_wait(bar_p(1, 1), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_pv(1, vslot.idx, pv_cnt[1] > 0);
+                    if constexpr (!kFp8) issue_pv(1, 0, vslot.idx, pv_cnt[1] > 0);
+                    issue_pv(1, 1, vslot.idx, true);
                     ++pv_cnt[1];
                 }
                 umma_commit(bar_empty(vslot.idx));
@@ -397,35 +416,111 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 return fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
                              fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             };
-            // The probabilities are computed against the running max right away; the block's own max
-            // is found alongside (it does not touch the exponent unit) and only if it exceeds the
-            // running max by more than the allowed lag -- rare after the first blocks -- is the block
-            // redone.  This keeps the max off the critical path.  The first block has no running max
-            // yet and takes its own first.
-            float alpha_total = 1.0f;
-            if (cnt == 0) {
-                m_run = row_max() * mult;
-            } else if (kFp8) {
-                // e4m3 leaves less than one binade of lag, so a speculative pass would be redone too
-                // often: take the block max first.
-                const float m_cand = row_max() * mult;
-                if (__any_sync(0xffffffffu, m_cand > m_run + kLag)) {
+            if constexpr (!kFp8) {
+                // The probabilities are computed against the running max right away; the block's own max
+                // is found alongside (it does not touch the exponent unit) and only if it exceeds the
+                // running max by more than the allowed lag -- rare after the first blocks -- is the block
+                // redone.  This keeps the max off the critical path.  The first block has no running max
+                // yet and takes its own first.
+                float alpha_total = 1.0f;
+                if (cnt == 0) m_run = row_max() * mult;
+                const uint64_t mult2 = pack2(mult, mult);
+                float sum = 0.0f;
+    #pragma unroll 1
+                for (int pass = 0; pass < 2; ++pass) {
+                    const float neg_m = kFp8 ? (kFp8PShiftLog2 + v_off - m_run) : -m_run;
+                    const uint64_t negm2 = pack2(neg_m, neg_m);
+                    uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
+    #pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t pk[kFp8 ? 8 : 16];
+    #pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            float e0, e1, e2, e3;
+                            unpack2(fma2(pack2(__uint_as_float(s[c][4 * i]), __uint_as_float(s[c][4 * i + 1])), mult2, negm2), e0, e1);
+                            e0 = ex2_approx(e0);
+                            e1 = ex2_approx(e1);
+                            unpack2(fma2(pack2(__uint_as_float(s[c][4 * i + 2]), __uint_as_float(s[c][4 * i + 3])), mult2, negm2), e2, e3);
+                            e2 = ex2_approx(e2);
+                            e3 = ex2_approx(e3);
+                            sum2[0] = add2(sum2[0], pack2(e0, e1));
+                            sum2[1] = add2(sum2[1], pack2(e2, e3));
+                            if constexpr (kFp8) {
+                                pk[i] = pack_quad_e4m3(e0, e1, e2, e3);
+                            } else {
+                                pk[2 * i] = pack_pair(e0, e1, kIn);
+                                pk[2 * i + 1] = pack_pair(e2, e3, kIn);
+                            }
+                        }
+                        if constexpr (kFp8) tmem_st8(taddr_s + c * 8, pk);
+                        else tmem_st16(taddr_s + c * 16, pk);
+                    }
+                    {
+                        float a, b;
+                        unpack2(add2(sum2[0], sum2[1]), a, b);
+                        sum = a + b;
+                    }
+                    if (pass == 1 || cnt == 0) break;
+                    const float m_cand = row_max() * mult;
+                    if (!__any_sync(0xffffffffu, m_cand > m_run + kLag)) break;
                     const float m_new = fmaxf(m_run, m_cand);
                     alpha_total = ex2_approx(m_run - m_new);
                     m_run = m_new;
                 }
-            }
-            const uint64_t mult2 = pack2(mult, mult);
-            float sum = 0.0f;
-#pragma unroll 1
-            for (int pass = 0; pass < 2; ++pass) {
+                const bool rescale = alpha_total != 1.0f;  // per thread; the warp-wide decision follows
+                l_run *= alpha_total;
+                // The scores are dead now; the (rare) rescale of O reuses their registers.
+                if (cnt > 0 && __any_sync(0xffffffffu, rescale)) {
+    #pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(taddr_o + c * 32, o);
+                        tmem_wait_ld();
+    #pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha_total);
+                        tmem_st32(taddr_o + c * 32, o);
+                    }
+                }
+                l_run += sum * l_fix;
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar_p(t, 1));
+            } else {
+                // e4m3 leaves less than one binade of lag, so a speculative pass would be redone too often:
+                // the block max is taken first.  In exchange the probabilities are handed over in two
+                // halves, so the first half of the P V product runs under the second half of the
+                // exponentials (the fp8 products are short; their latency matters more than for bf16).
+                const float m_cand = row_max() * mult;
+                const bool rescale = __any_sync(0xffffffffu, m_cand > m_run + kLag);
+                float alpha = 1.0f;
+                if (rescale) {
+                    const float m_new = fmaxf(m_run, m_cand);
+                    alpha = ex2_approx(m_run - m_new);  // 0 on the first block (m_run = -inf)
+                    l_run *= alpha;
+                    m_run = m_new;
+                    // The (rare, after the first blocks) rescale of O must be over before the first half
+                    // of P is handed to the MMA thread.  The scores of this block were issued behind the
+                    // previous P V product, so that product has finished.
+                    if (cnt > 0) {  // eight columns at a time: the scores are live, registers are scarce here
+    #pragma unroll 1
+                        for (int c = 0; c < kHeadDim / 8; ++c) {
+                            uint32_t o[8];
+                            tmem_ld8(taddr_o + c * 8, o);
+                            tmem_wait_ld();
+    #pragma unroll
+                            for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st8(taddr_o + c * 8, o);
+                        }
+                    }
+                }
+                // x = s * mult - m as packed pairs (one instruction per two scores), then ex2 and pack.
                 const float neg_m = kFp8 ? (kFp8PShiftLog2 + v_off - m_run) : -m_run;
-                const uint64_t negm2 = pack2(neg_m, neg_m);
+                const uint64_t mult2 = pack2(mult, mult), negm2 = pack2(neg_m, neg_m);
                 uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
-#pragma unroll
+    #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t pk[kFp8 ? 8 : 16];
-#pragma unroll
+    #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         float e0, e1, e2, e3;
                         unpack2(fma2(pack2(__uint_as_float(s[c][4 * i]), __uint_as_float(s[c][4 * i + 1])), mult2, negm2), e0, e1);
@@ -445,37 +540,18 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     }
                     if constexpr (kFp8) tmem_st8(taddr_s + c * 8, pk);
                     else tmem_st16(taddr_s + c * 16, pk);
+                    if (c & 1) {  // a half of the block's keys is complete: hand it over
+                        tmem_wait_st();
+                        tc_fence_before();
+                        mbar_arrive(bar_p(t, c >> 1));
+                    }
                 }
                 {
                     float a, b;
                     unpack2(add2(sum2[0], sum2[1]), a, b);
-                    sum = a + b;
-                }
-                if (pass == 1 || cnt == 0 || kFp8) break;
-                const float m_cand = row_max() * mult;
-                if (!__any_sync(0xffffffffu, m_cand > m_run + kLag)) break;
-                const float m_new = fmaxf(m_run, m_cand);
-                alpha_total = ex2_approx(m_run - m_new);
-                m_run = m_new;
-            }
-            const bool rescale = alpha_total != 1.0f;  // per thread; the warp-wide decision follows
-            l_run *= alpha_total;
-            // The scores are dead now; the (rare) rescale of O reuses their registers.
-            if (cnt > 0 && __any_sync(0xffffffffu, rescale)) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t o[32];
-                    tmem_ld32(taddr_o + c * 32, o);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha_total);
-                    tmem_st32(taddr_o + c * 32, o);
+                    l_run += (a + b) * l_fix;
                 }
             }
-            l_run += sum * l_fix;
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar_p(t));
             ++cnt;
         }
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_s(t), static_cast<uint32_t>(cnt) & 1u, abort_flag, 26 + t));
