@@ -9,7 +9,7 @@ GPU) runs the same layer sequence-parallel with the Ulysses wrapper, so the tota
 line.  Inputs are seeded synthetic tensors of the named shapes (no dataset exists for this path);
 3.1 GB of operands per step exceed the 126 MB L2, so no L2 flush is needed between steps.
 
-Other single-GPU workloads of the same path (`--workload sparse|fp8|mask|quant|rearrange|c2`) print the
+Other single-GPU workloads of the same path (`--workload sparse|sparse_layer|fp8|fp8_layer|mask|quant|rearrange|c2`) print the
 same kind of line for their kernel; `--impl reference` times the CPU oracle (the reference's
 unfused torch formula) on the host cores for the same metric.
 """
@@ -285,7 +285,7 @@ def single_gpu_workload(args, device):
     cfg = workloads.C3
     peaks = measured_peaks()
     name = args.workload
-    src = workloads.C4 if name in ("fp8", "quant") else (workloads.C2 if name == "c2" else cfg)
+    src = workloads.C4 if name in ("fp8", "fp8_layer", "quant") else (workloads.C2 if name == "c2" else cfg)
     if args.heads:
         cfg = workloads.Config(cfg.name, cfg.batch, args.heads, cfg.grid, cfg.seq, cfg.dtype)
     q, k, v = workloads.make_qkv(src, device, seed=0, heads=args.heads or None)
@@ -307,6 +307,24 @@ def single_gpu_workload(args, device):
         extra = {"block_density": density, "sparsity_arg": args.sparsity, "temporal_band": args.band,
                  "executed_tflop": cfg.flops * density / 1e12}
         label = "RainFusion block-sparse attention (mask prebuilt, tokens pre-permuted), B1 N40 S75600 D128"
+    elif name == "sparse_layer":
+        # The whole RainFusion layer through the public API, every step: mask builder, three
+        # permutations, block-sparse attention, inverse permutation.
+        from mindiesd import sparse_attention
+        step = lambda: sparse_attention(q, k, v, head_num=cfg.heads, input_layout="BNSD", sparse_type="rf_v3",  # noqa: E731
+                                        block_size=128, latent_shape_q=cfg.grid, latent_shape_k=cfg.grid,
+                                        sparsity=args.sparsity)
+        work, unit, launches = cfg.flops, "TFLOP/s", 7
+        label = ("RainFusion layer via mindiesd.sparse_attention(rf_v3): mask + permute + sparse attention + inverse, "
+                 "B1 N40 S75600 D128")
+        extra = {"sparsity_arg": args.sparsity}
+    elif name == "fp8_layer":
+        # The whole FP8 layer through the public hook: rotate + quantise q, k, v, then FP8 attention.
+        from mindiesd import FP8RotateQuantFA
+        hook = FP8RotateQuantFA(v_per_channel=True).to(device)
+        step = lambda: hook(q, k, v, layout="BNSD")  # noqa: E731
+        work, unit, launches = cfg.flops, "TFLOP/s", 6
+        label = "FP8 layer via mindiesd.FP8RotateQuantFA: Hadamard + e4m3 quantisation of q, k, v + FP8 attention, B1 N40 S75600 D128"
     elif name == "fp8":
         q8, qs = _cabi.fa_block_quant(q, 128, rotate=True)
         k8, ks = _cabi.fa_block_quant(k, 128, rotate=True)
@@ -347,7 +365,7 @@ def single_gpu_workload(args, device):
         "metric": "attention_dense_equiv_tflops" if unit == "TFLOP/s" else "achieved_hbm_gbs", "value": value,
         "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "e4m3" if name == "fp8" else "bf16", "data": "synthetic",
+        "dtype": "e4m3" if name in ("fp8", "fp8_layer") else "bf16", "data": "synthetic",
         "config": dict({"workload": label + (f" [heads reduced to {args.heads}]" if args.heads else ""), "l2": "operands exceed L2; no flush", "kernel_status": _cabi.device_status()}, **extra),
         "clocks": clocks,
         "roofline": {"bound": bound, "achieved": value, "peak": peak, "unit": unit, "frac": value / peak, "traffic": None,
