@@ -38,11 +38,9 @@ __device__ __forceinline__ void hadamard128(float (&f)[8], int c) {
             }
 #pragma unroll
     for (int m = 1; m < 16; m <<= 1) {
+        const float sign = (c & m) ? -1.0f : 1.0f;  // upper lane of a pair: other - mine
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float other = __shfl_xor_sync(0xffffffffu, f[i], m);
-            f[i] = (c & m) ? other - f[i] : f[i] + other;
-        }
+        for (int i = 0; i < 8; ++i) f[i] = fmaf(f[i], sign, __shfl_xor_sync(0xffffffffu, f[i], m));
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) f[i] *= 0.08838834764831845f;
@@ -76,7 +74,10 @@ __device__ __forceinline__ uint2 quant8(const float (&f)[8], float inv) {
 }
 
 // mode 0.  Grid (row block, head, batch); 256 threads = 16 token rows x 16 vectors of 8 channels.
-// The block is read twice; the second read is served by L2.
+// kTrips = row_block / 16 rows per thread.  kKeep: the rotated block stays in registers between the
+// absmax pass and the quantise pass, so the input is read and rotated once; otherwise the block is
+// read twice, the second time from L2.
+template <int kTrips, bool kKeep>
 __global__ void __launch_bounds__(256) quant_block_kernel(const QuantParams p) {
     __shared__ float warp_max[8];
     const int blk = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
@@ -84,16 +85,21 @@ __global__ void __launch_bounds__(256) quant_block_kernel(const QuantParams p) {
     const int first = blk * p.row_block;
     const int count = min(p.row_block, p.seq - first);
     const uint16_t* base = static_cast<const uint16_t*>(p.x) + batch * p.stride[0] + head * p.stride[1];
+    float kept[kKeep ? kTrips : 1][8];
     float amax = 0.0f;
-    for (int rr = 0; rr < p.row_block; rr += 16) {  // uniform trip count: the rotation shuffles across lanes
-        const int r = rr + r0;
+#pragma unroll
+    for (int tr = 0; tr < kTrips; ++tr) {  // uniform trip count: the rotation shuffles across lanes
+        const int r = tr * 16 + r0;
         uint4 raw = make_uint4(0, 0, 0, 0);
         if (r < count) raw = *reinterpret_cast<const uint4*>(base + (first + r) * p.stride[2] + c * 8);
         float f[8];
         unpack8(raw, p.is_bf16, f);
         if (p.rotate) hadamard128(f, c);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+        for (int i = 0; i < 8; ++i) {
+            amax = fmaxf(amax, fabsf(f[i]));
+            if constexpr (kKeep) kept[tr][i] = f[i];
+        }
     }
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
@@ -107,13 +113,19 @@ __global__ void __launch_bounds__(256) quant_block_kernel(const QuantParams p) {
     if (threadIdx.x == 0)
         p.scales[(static_cast<int64_t>(batch) * p.heads + head) * p.blocks + blk] = scale;
     uint8_t* obase = p.out + ((static_cast<int64_t>(batch) * p.heads + head) * p.seq) * 128;
-    for (int rr = 0; rr < p.row_block; rr += 16) {
-        const int r = rr + r0;
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (r < count) raw = *reinterpret_cast<const uint4*>(base + (first + r) * p.stride[2] + c * 8);
+#pragma unroll
+    for (int tr = 0; tr < kTrips; ++tr) {
+        const int r = tr * 16 + r0;
         float f[8];
-        unpack8(raw, p.is_bf16, f);
-        if (p.rotate) hadamard128(f, c);
+        if constexpr (kKeep) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = kept[tr][i];
+        } else {
+            uint4 raw = make_uint4(0, 0, 0, 0);
+            if (r < count) raw = *reinterpret_cast<const uint4*>(base + (first + r) * p.stride[2] + c * 8);
+            unpack8(raw, p.is_bf16, f);
+            if (p.rotate) hadamard128(f, c);
+        }
         if (r < count) *reinterpret_cast<uint2*>(obase + static_cast<int64_t>(first + r) * 128 + c * 8) = quant8(f, inv);
     }
 }
@@ -207,7 +219,13 @@ extern "C" int mindiesd_fa_block_quant(const mindiesd_quant_args* a, void* strea
         p.row_block = a->row_block;
         p.blocks = (a->seq + a->row_block - 1) / a->row_block;
         dim3 grid(p.blocks, a->heads, a->batch);
-        quant_block_kernel<<<grid, 256, 0, stream>>>(p);
+        // Keeping the block in registers pays when the rotation would otherwise be done twice; without
+        // the rotation the lighter two-pass form (second read from L2) runs at copy speed.
+        if (a->rotate && a->row_block == 128) quant_block_kernel<8, true><<<grid, 256, 0, stream>>>(p);
+        else if (a->rotate && a->row_block == 256) quant_block_kernel<16, true><<<grid, 256, 0, stream>>>(p);
+        else if (a->row_block == 128) quant_block_kernel<8, false><<<grid, 256, 0, stream>>>(p);
+        else if (a->row_block == 256) quant_block_kernel<16, false><<<grid, 256, 0, stream>>>(p);
+        else quant_block_kernel<32, false><<<grid, 256, 0, stream>>>(p);
     } else if (a->mode == 1) {
         p.row_block = 0;
         p.blocks = 0;

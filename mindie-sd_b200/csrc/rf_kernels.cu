@@ -75,19 +75,39 @@ struct RearrangeParams {
     int inverse;
 };
 
+constexpr int kRearrangeRows = 128;  // token rows one CTA moves
+
 __global__ void __launch_bounds__(256) rf_rearrange_kernel(const RearrangeParams p) {
-    const int rows_per_cta = 256 / p.vec_per_row;
-    const int v = threadIdx.x % p.vec_per_row;
-    const int r = threadIdx.x / p.vec_per_row;
+    // The source index of a position costs several integer divisions: it is computed once per row
+    // (not once per 16-byte lane) and shared through shared memory.
+    __shared__ int src_tok[kRearrangeRows];
     const int head = blockIdx.y % p.heads;
     const int batch = blockIdx.y / p.heads;
-    const int pos = blockIdx.x * rows_per_cta + r;  // position in the permuted order
-    if (r >= rows_per_cta || pos >= p.seq) return;
-    const int src_tok = source_of(p.g, pos);
-    const int from = p.inverse ? pos : src_tok;
-    const int to = p.inverse ? src_tok : pos;
-    const uint4 val = p.src[batch * p.src_stride[0] + head * p.src_stride[1] + from * p.src_stride[2] + v];
-    p.dst[batch * p.dst_stride[0] + head * p.dst_stride[1] + to * p.dst_stride[2] + v] = val;
+    const int pos0 = blockIdx.x * kRearrangeRows;  // first position (permuted order) of this CTA
+    const int nrows = min(kRearrangeRows, p.seq - pos0);
+    if (threadIdx.x < nrows) src_tok[threadIdx.x] = source_of(p.g, pos0 + threadIdx.x);
+    __syncthreads();
+    const uint4* src = p.src + batch * p.src_stride[0] + head * p.src_stride[1];
+    uint4* dst = p.dst + batch * p.dst_stride[0] + head * p.dst_stride[1];
+    const int total = nrows * p.vec_per_row;
+    // Four vectors per thread and trip: the loads are issued before the stores.
+    for (int i0 = threadIdx.x; i0 < total; i0 += 4 * 256) {
+        uint4 val[4];
+        int64_t to[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * 256;
+            if (i < total) {
+                const int r = i / p.vec_per_row, v = i - r * p.vec_per_row;
+                const int a = pos0 + r, b = src_tok[r];
+                val[u] = src[static_cast<int64_t>(p.inverse ? a : b) * p.src_stride[2] + v];
+                to[u] = static_cast<int64_t>(p.inverse ? b : a) * p.dst_stride[2] + v;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i0 + u * 256 < total) dst[to[u]] = val[u];
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -407,8 +427,7 @@ extern "C" int mindiesd_rf_rearrange(const mindiesd_rearrange_args* a, void* str
     p.vec_per_row = a->head_dim / vec;
     p.g = make_grid(a->t, a->h, a->w, a->txt_len);
     p.inverse = a->inverse ? 1 : 0;
-    const int rows_per_cta = 256 / p.vec_per_row;
-    dim3 grid((a->seq + rows_per_cta - 1) / rows_per_cta, a->batch * a->heads);
+    dim3 grid((a->seq + kRearrangeRows - 1) / kRearrangeRows, a->batch * a->heads);
     rf_rearrange_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? MINDIESD_OK : static_cast<int>(e);
