@@ -252,7 +252,7 @@ __device__ __forceinline__ unsigned long long order_key(double v) {
 }
 
 constexpr int kMaskRows = 8;    // q blocks per CTA = M of the fp64 tensor-core tile
-constexpr int kMaskTile = 32;   // k blocks staged per trip
+constexpr int kMaskTile = 64;   // k blocks staged per trip: eight per warp
 
 __device__ __forceinline__ void dmma884(double& c0, double& c1, double a, double b) {
     asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};"
@@ -265,14 +265,13 @@ __device__ __forceinline__ void dmma884(double& c0, double& c1, double a, double
 template <int kKeysPerLane>
 __global__ void __launch_bounds__(256) rf_mask_kernel(const MaskParams p) {
     extern __shared__ unsigned char smem_dyn[];
-    // layout (8-byte units): q rows [8][dim + 4] | k tile [32][dim + 4] | partial sums [4][64] |
-    // keys [8][blocks].  q and k are widened to fp64 once when staged.  The pitch dim + 4 makes the
-    // tensor-core fragment loads (8 rows x 4 consecutive channels) hit 32 distinct 8-byte slots.
+    // layout: q rows [8][dim + 4] fp64 | keys [8][blocks] u64 | k tile [64][dim + 4] fp32.
+    // q is widened to fp64 once; k is staged as it lies (fp32) and widened in the fragment load.  The
+    // pitch dim + 4 makes both fragment loads (8 rows x 4 consecutive channels) conflict-free.
     const int pitch = p.dim + 4;
     double* sq = reinterpret_cast<double*>(smem_dyn);
-    double* sk = sq + kMaskRows * pitch;
-    double* part = sk + kMaskTile * pitch;
-    unsigned long long* keys = reinterpret_cast<unsigned long long*>(part + 4 * 64);
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(sq + kMaskRows * pitch);
+    float* sk = reinterpret_cast<float*>(keys + static_cast<size_t>(kMaskRows) * p.blocks);
 
     const int row0 = blockIdx.x * kMaskRows, head = blockIdx.y, batch = blockIdx.z;
     const int nrows = min(kMaskRows, p.blocks - row0);
@@ -282,52 +281,44 @@ __global__ void __launch_bounds__(256) rf_mask_kernel(const MaskParams p) {
 
     // Staging: dim is a power of two; a thread moves 4 consecutive channels (one 16-byte load).
     const int vec_per_row = p.dim >> 2, vshift = p.vec_shift;  // vec_per_row == 1 << vshift
-    auto stage = [&](double* dst, const float* src, int rows_total, int rows_valid) {
-        for (int i = tid; i < rows_total * vec_per_row; i += 256) {
-            const int r = i >> vshift, v = i & (vec_per_row - 1);
-            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (r < rows_valid) x = *reinterpret_cast<const float4*>(src + static_cast<int64_t>(r) * p.dim + v * 4);
-            double2* d = reinterpret_cast<double2*>(dst + r * pitch + v * 4);
-            d[0] = make_double2(static_cast<double>(x.x), static_cast<double>(x.y));
-            d[1] = make_double2(static_cast<double>(x.z), static_cast<double>(x.w));
-        }
-    };
-    stage(sq, qp + static_cast<int64_t>(row0) * p.dim, kMaskRows, nrows);
+    for (int i = tid; i < kMaskRows * vec_per_row; i += 256) {
+        const int r = i >> vshift, v = i & (vec_per_row - 1);
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < nrows) x = *reinterpret_cast<const float4*>(qp + static_cast<int64_t>(row0 + r) * p.dim + v * 4);
+        double2* d = reinterpret_cast<double2*>(sq + r * pitch + v * 4);
+        d[0] = make_double2(static_cast<double>(x.x), static_cast<double>(x.y));
+        d[1] = make_double2(static_cast<double>(x.z), static_cast<double>(x.w));
+    }
 
-    // Scores on the fp64 tensor cores: warp (cg, half) owns k columns 8cg..8cg+7 of the tile and one
-    // half of the channels; the two halves are added through shared memory.
-    const int cg = warp & 3, half = warp >> 2;
-    const int ch_begin = half * (p.dim >> 1), ch_end = ch_begin + (p.dim >> 1);
+    // Scores on the fp64 tensor cores: warp w owns k columns 8w..8w+7 of the tile over all channels,
+    // as four independent accumulator chains (consecutive MMAs of one chain wait on each other).
     const int frag_row = lane >> 2, frag_k = lane & 3;
     for (int j0 = 0; j0 < p.blocks; j0 += kMaskTile) {
         __syncthreads();
         const int nj = min(kMaskTile, p.blocks - j0);
-        stage(sk, kp + static_cast<int64_t>(j0) * p.dim, kMaskTile, nj);
+        for (int i = tid; i < kMaskTile * vec_per_row; i += 256) {
+            const int r = i >> vshift, v = i & (vec_per_row - 1);
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < nj) x = *reinterpret_cast<const float4*>(kp + static_cast<int64_t>(j0 + r) * p.dim + v * 4);
+            *reinterpret_cast<float4*>(sk + r * pitch + v * 4) = x;
+        }
         __syncthreads();
-        double c0 = 0.0, c1 = 0.0, d0 = 0.0, d1 = 0.0;  // two chains, so consecutive MMAs do not wait on each other
+        double c[4][2] = {{0.0, 0.0}, {0.0, 0.0}, {0.0, 0.0}, {0.0, 0.0}};
         const double* a_ptr = sq + frag_row * pitch + frag_k;
-        const double* b_ptr = sk + (cg * 8 + frag_row) * pitch + frag_k;
-        int ch = ch_begin;
-        for (; ch + 8 <= ch_end; ch += 8) {
-            dmma884(c0, c1, a_ptr[ch], b_ptr[ch]);
-            dmma884(d0, d1, a_ptr[ch + 4], b_ptr[ch + 4]);
+        const float* b_ptr = sk + (warp * 8 + frag_row) * pitch + frag_k;
+        int ch = 0;
+        for (; ch + 16 <= p.dim; ch += 16) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                dmma884(c[u][0], c[u][1], a_ptr[ch + 4 * u], static_cast<double>(b_ptr[ch + 4 * u]));
         }
-        for (; ch < ch_end; ch += 4) dmma884(c0, c1, a_ptr[ch], b_ptr[ch]);
-        c0 += d0;
-        c1 += d1;
-        if (half == 1) {
-            part[cg * 64 + lane * 2] = c0;
-            part[cg * 64 + lane * 2 + 1] = c1;
-        }
-        __syncthreads();
-        if (half == 0) {
-            c0 += part[cg * 64 + lane * 2];
-            c1 += part[cg * 64 + lane * 2 + 1];
-            const int col = j0 + cg * 8 + frag_k * 2;
-            if (frag_row < nrows) {
-                if (col < p.blocks) keys[static_cast<size_t>(frag_row) * p.blocks + col] = order_key(c0);
-                if (col + 1 < p.blocks) keys[static_cast<size_t>(frag_row) * p.blocks + col + 1] = order_key(c1);
-            }
+        for (; ch < p.dim; ch += 4) dmma884(c[0][0], c[0][1], a_ptr[ch], static_cast<double>(b_ptr[ch]));
+        const double s0 = (c[0][0] + c[1][0]) + (c[2][0] + c[3][0]);
+        const double s1 = (c[0][1] + c[1][1]) + (c[2][1] + c[3][1]);
+        const int col = j0 + warp * 8 + frag_k * 2;
+        if (frag_row < nrows) {
+            if (col < p.blocks) keys[static_cast<size_t>(frag_row) * p.blocks + col] = order_key(s0);
+            if (col + 1 < p.blocks) keys[static_cast<size_t>(frag_row) * p.blocks + col + 1] = order_key(s1);
         }
     }
     __syncthreads();
@@ -342,15 +333,46 @@ __global__ void __launch_bounds__(256) rf_mask_kernel(const MaskParams p) {
             const int j = lane + 32 * i;
             mine[i] = j < p.blocks ? kr[j] : 0ull;
         }
-        unsigned long long thr = 0;
-        for (int bit = 63; bit >= 0; --bit) {
-            const unsigned long long cand = thr | (1ull << bit);
+        // High words first (32 steps on 32-bit compares); the low words only matter among the keys that
+        // share the threshold's high word, which is almost always a single key.
+        unsigned int thr_hi = 0;
+        for (int bit = 31; bit >= 0; --bit) {
+            const unsigned int cand = thr_hi | (1u << bit);
             int cnt = 0;
 #pragma unroll
-            for (int i = 0; i < kKeysPerLane; ++i) cnt += mine[i] >= cand;
+            for (int i = 0; i < kKeysPerLane; ++i) cnt += static_cast<unsigned int>(mine[i] >> 32) >= cand;
             cnt = __reduce_add_sync(0xffffffffu, cnt);
-            if (cnt >= p.keep_len) thr = cand;
+            if (cnt >= p.keep_len) thr_hi = cand;
         }
+        int above = 0, equal = 0;
+#pragma unroll
+        for (int i = 0; i < kKeysPerLane; ++i) {
+            const unsigned int hi = static_cast<unsigned int>(mine[i] >> 32);
+            above += hi > thr_hi;
+            equal += hi == thr_hi;
+        }
+        above = __reduce_add_sync(0xffffffffu, above);
+        equal = __reduce_add_sync(0xffffffffu, equal);
+        unsigned int thr_lo = 0;
+        if (equal == 1) {
+            unsigned int lo = 0;
+#pragma unroll
+            for (int i = 0; i < kKeysPerLane; ++i)
+                if (static_cast<unsigned int>(mine[i] >> 32) == thr_hi) lo = static_cast<unsigned int>(mine[i]);
+            thr_lo = __reduce_or_sync(0xffffffffu, lo);
+        } else {
+            const int want = p.keep_len - above;  // rank of the threshold among the keys that tie on the high word
+            for (int bit = 31; bit >= 0; --bit) {
+                const unsigned int cand = thr_lo | (1u << bit);
+                int cnt = 0;
+#pragma unroll
+                for (int i = 0; i < kKeysPerLane; ++i)
+                    cnt += static_cast<unsigned int>(mine[i] >> 32) == thr_hi && static_cast<unsigned int>(mine[i]) >= cand;
+                cnt = __reduce_add_sync(0xffffffffu, cnt);
+                if (cnt >= want) thr_lo = cand;
+            }
+        }
+        const unsigned long long thr = (static_cast<unsigned long long>(thr_hi) << 32) | thr_lo;
         const int qb = row0 + r;
         const bool row_forced = qb >= p.blocks - p.txt_blocks || qb < p.first_frame_blocks;
         // Frame range of the q block (image blocks only), for the optional temporal band.
@@ -391,7 +413,8 @@ __global__ void __launch_bounds__(256) rf_mask_kernel(const MaskParams p) {
 }
 
 size_t mask_smem_bytes(int dim, int blocks) {
-    return (static_cast<size_t>(kMaskRows + kMaskTile) * (dim + 4) + 4 * 64 + static_cast<size_t>(kMaskRows) * blocks) * 8;
+    return (static_cast<size_t>(kMaskRows) * (dim + 4) + static_cast<size_t>(kMaskRows) * blocks) * 8 +
+           static_cast<size_t>(kMaskTile) * (dim + 4) * 4;
 }
 
 }  // namespace
