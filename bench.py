@@ -9,7 +9,7 @@ GPU) runs the same layer sequence-parallel with the Ulysses wrapper, so the tota
 line.  Inputs are seeded synthetic tensors of the named shapes (no dataset exists for this path);
 3.1 GB of operands per step exceed the 126 MB L2, so no L2 flush is needed between steps.
 
-Other single-GPU workloads of the same path (`--workload sparse|sparse_layer|fp8|fp8_layer|mask|quant|rearrange|c2`) print the
+Other single-GPU workloads of the same path (`--workload sparse|sparse_layer|fp8|fp8_layer|mask|quant|rearrange|estimate|ada_layer|c2`) print the
 same kind of line for their kernel; `--impl reference` times the CPU oracle (the reference's
 unfused torch formula) on the host cores for the same metric.
 """
@@ -347,6 +347,31 @@ def single_gpu_workload(args, device):
         work = q.numel() * 3.0  # 2 bytes in, 1 byte out per element
         unit, bound = "GB/s", "hbm"
         label = "e4m3 block quantisation with Hadamard rotation of one operand, B1 N40 S75600 D128"
+    elif name == "estimate":
+        # The ada_bsa mask builder: a K = 1024 contraction per pair of 8-token groups on the tensor cores,
+        # softmax and 16 x 16 block sums, then the cumulative-mass decision.
+        scratch = torch.empty(_cabi.lib().mindiesd_sparse_block_estimate_scratch_bytes(1, cfg.heads, cfg.seq),
+                              dtype=torch.uint8, device=device)
+        step = lambda: _cabi.sparse_block_estimate(q, k, HEAD_DIM ** -0.5 / 8, args.cdf, 1.0 - args.sparsity,  # noqa: E731
+                                                   scratch=scratch)
+        groups = cfg.seq // 8
+        work, unit = 2.0 * cfg.heads * groups * groups * 8 * HEAD_DIM, "TFLOP/s"
+        launches = 2 * ((cfg.heads + 3) // 4)
+        label = f"ada_bsa sparse block estimate, B1 N{cfg.heads} S75600 D128, cdf threshold {args.cdf}"
+        extra = {"flops_per_step": work, "metric_note": "TFLOP/s of the estimator's own contraction, not dense-equivalent"}
+    elif name == "ada_layer":
+        from mindiesd import sparse_attention
+        step = lambda: sparse_attention(q, k, v, head_num=cfg.heads, input_layout="BNSD", sparse_type="ada_bsa",  # noqa: E731
+                                        block_size=128, cdf_threshold=args.cdf, sparsity=args.sparsity)
+        work, unit, launches = cfg.flops, "TFLOP/s", 2 * ((cfg.heads + 3) // 4) + 1
+        from mindiesd.layers.flash_attn.sparse_flash_attn_ada_bsa import get_estimate_mask
+        smask, _ = get_estimate_mask(q, k, v, scale=HEAD_DIM ** -0.5, head_num=cfg.heads, sparsity=args.sparsity,
+                                     cdf_threshold=args.cdf)
+        extra = {"block_density": smask[..., :591].float().mean().item(), "cdf_threshold": args.cdf,
+                 "sparsity_arg": args.sparsity}
+        del smask
+        label = ("ada_bsa layer via mindiesd.sparse_attention(ada_bsa): block estimate + block-sparse attention, "
+                 "B1 N40 S75600 D128")
     elif name == "rearrange":
         step = lambda: _cabi.rf_rearrange(q, cfg.grid, 0, True)  # noqa: E731
         work = q.numel() * 4.0
@@ -383,6 +408,7 @@ def main():
     ap.add_argument("--workload", default="dense")
     ap.add_argument("--sparsity", type=float, default=0.75)
     ap.add_argument("--band", type=int, default=-1)
+    ap.add_argument("--cdf", type=float, default=0.9, help="cumulative-mass threshold of the ada_bsa estimate")
     ap.add_argument("--heads", type=int, default=0, help="reduced head count for profiler captures (default: the full 40)")
     ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs (profiler captures)")
     args = ap.parse_args()

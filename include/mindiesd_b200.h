@@ -251,6 +251,57 @@ typedef struct mindiesd_quant_args {
 int mindiesd_fa_block_quant(const mindiesd_quant_args* args, void* stream);
 
 /*
+ * Sparse block estimate: the mask builder of adaptive block-sparse attention ("ada_bsa").
+ *
+ * Tokens are taken `stride` (8) at a time; the pooled logit of query group g and key group h is
+ * scale * sum_i q[8g + 7 - i] . k[8h + i].  Each row of pooled logits goes through a softmax over
+ * all key groups; the probabilities are summed over the 16 x 16 groups of every 128 x 128 token
+ * block.  Per query block, with the last key block's mass cleared (keep_recent), the heaviest key
+ * blocks are kept until their running sum reaches `threshold` of the row's total -- at most
+ * int(row_sparse * blocks) of them when row_sparse * blocks is smaller than that prefix -- together
+ * with every block as heavy as the last one kept, the first block (keep_sink) and the last block
+ * (keep_recent).
+ *
+ *   q, k:   bf16 or fp16, addressed [batch, head, token, channel] through element strides
+ *   seq:    a multiple of 8 (the golden pads the last group with zero tokens; a caller with a
+ *           ragged sequence does the same before the call)
+ *   mask:   int8 [batch, heads, blocks, mask_cols], mask_cols >= blocks (the reference rounds it
+ *           up to a multiple of 32); columns >= blocks are written 0
+ *   count:  int32 [batch, heads, blocks]: kept blocks per row
+ *   scratch: at least mindiesd_sparse_block_estimate_scratch_bytes(1, 1, seq) bytes (one head per
+ *           pass); the size that function returns for the real batch and heads lets four heads
+ *           run per pass, whose partial sums stay in L2
+ * causal != 0 is not supported (MINDIESD_E_VALUE).
+ *
+ * Stands in for: aclnnSparseBlockEstimate as registered in csrc/plugin/register_ops.cpp:46-53 and
+ * called by mindiesd/layers/flash_attn/sparse_flash_attn_ada_bsa.py:31-47; semantics pinned by
+ * sparse_estimate_cpu, tests/plugin/test_sparseblockestimate.py:49-145.
+ */
+typedef struct mindiesd_estimate_args {
+    const void* q;
+    const void* k;
+    int64_t q_stride[3]; /* elements: batch, head, token */
+    int64_t k_stride[3];
+    int32_t dtype; /* MINDIESD_BF16 / MINDIESD_FP16 */
+    int32_t batch, heads, kv_heads, seq, head_dim; /* head_dim 64 or 128 */
+    int32_t stride;      /* 8 */
+    int32_t sparse_size; /* 128 */
+    float scale;         /* multiplies the pooled dot product; the layer passes softmax_scale / stride */
+    float threshold;     /* share of a row's mass the kept prefix must reach */
+    double row_sparse;   /* cap on the kept prefix as a share of the row; <= 0 or >= 1: no cap */
+    int32_t causal;      /* must be 0 */
+    int32_t keep_sink, keep_recent;
+    int8_t* mask;
+    int32_t mask_cols;
+    int32_t* count;
+    void* scratch;
+    size_t scratch_bytes;
+} mindiesd_estimate_args;
+
+size_t mindiesd_sparse_block_estimate_scratch_bytes(int32_t batch, int32_t heads, int32_t seq);
+int mindiesd_sparse_block_estimate(const mindiesd_estimate_args* args, void* stream);
+
+/*
  * Device status word of the current device: 0, or the code of the first bounded wait inside a
  * kernel that gave up since the last call.  Synchronises the device; clears the word.
  */

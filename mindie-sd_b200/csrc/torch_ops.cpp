@@ -1,5 +1,5 @@
-// torch.ops.mindiesd.* for CUDA tensors.  The three attention schemas are those of MindIE-SD's
-// own operator library (csrc/plugin/register_ops.cpp:27-32, 41-45, 62-67), argument names
+// torch.ops.mindiesd.* for CUDA tensors.  The attention and estimator schemas are those of MindIE-SD's
+// own operator library (csrc/plugin/register_ops.cpp:27-32, 41-67), argument names
 // included, because callers pass every argument by keyword.  Each implementation checks its
 // arguments, allocates its outputs from torch's caching allocator, and calls one extern "C"
 // launcher of libmindiesd_b200.so on the current stream; nothing synchronises.
@@ -274,6 +274,111 @@ std::tuple<at::Tensor, at::Tensor> rainfusionattention_cuda(
     return std::make_tuple(out, lse);
 }
 
+// ---- ada_bsa: cumulative-mass mask estimate and attention over the kept blocks -------------------------
+// Views a BNSD / BSND / BSH tensor as 4-D and reports whether heads come first.
+at::Tensor view_4d(const at::Tensor& t, const std::string& layout, int64_t heads, bool* head_first, const char* op) {
+    if (layout == "BNSD" || layout == "BSND") {
+        TORCH_CHECK(t.dim() == 4, op, ": ", layout, " tensors are 4-D");
+        *head_first = layout == "BNSD";
+        return t;
+    }
+    TORCH_CHECK(layout == "BSH", op, ": input_layout only supports BNSD, BSND and BSH, got ", layout);
+    TORCH_CHECK(t.dim() == 3 && heads > 0 && t.size(2) % heads == 0, op, ": BSH tensors are 3-D with H = N * D");
+    *head_first = false;
+    return t.view({t.size(0), t.size(1), heads, t.size(2) / heads});
+}
+
+std::tuple<at::Tensor, at::Tensor> sparse_block_estimate_cuda(
+    const at::Tensor& query, const at::Tensor& key, c10::OptionalIntArrayRef actual_seq_lengths,
+    c10::OptionalIntArrayRef actual_seq_lengths_kv, std::string input_layout, int64_t stride, int64_t sparse_size,
+    int64_t num_heads, int64_t num_key_value_heads, double scale_value, double threshold, bool causal, bool keep_sink,
+    bool keep_recent, double row_sparse) {
+    TORCH_CHECK(num_heads != 0, "num_heads must be nonzero.");
+    TORCH_CHECK(sparse_size != 0, "sparse_size must be nonzero.");
+    TORCH_CHECK(query.is_cuda() && key.is_cuda(), "sparse_block_estimate: query and key must be CUDA tensors");
+    TORCH_CHECK(query.scalar_type() == key.scalar_type(), "sparse_block_estimate: query and key must share a dtype");
+    TORCH_CHECK(!actual_seq_lengths.has_value() && !actual_seq_lengths_kv.has_value(),
+                "sparse_block_estimate: actual_seq_lengths are not supported");
+    TORCH_CHECK(!causal, "sparse_block_estimate: causal=True is not supported");
+    TORCH_CHECK(stride == 8 && sparse_size == 128, "sparse_block_estimate: only stride=8 and sparse_size=128 are supported");
+    bool head_first = true, head_first_k = true;
+    at::Tensor q4 = view_4d(query, input_layout, num_heads, &head_first, "sparse_block_estimate");
+    at::Tensor k4 = view_4d(key, input_layout, num_key_value_heads, &head_first_k, "sparse_block_estimate");
+    const int sdim = head_first ? 2 : 1, ndim = head_first ? 1 : 2;
+    const int64_t b = q4.size(0), nq = q4.size(ndim), s = q4.size(sdim), d = q4.size(3);
+    TORCH_CHECK(k4.size(0) == b && k4.size(sdim) == s && k4.size(3) == d && nq % k4.size(ndim) == 0,
+                "sparse_block_estimate: key must have the query's batch, length and head size");
+    // A ragged last group is completed with zero tokens, as the reference's golden does.
+    if (s % 8) {
+        const int64_t pad = 8 - s % 8;
+        std::vector<int64_t> pads = head_first ? std::vector<int64_t>{0, 0, 0, pad} : std::vector<int64_t>{0, 0, 0, 0, 0, pad};
+        q4 = at::constant_pad_nd(q4, pads, 0);
+        k4 = at::constant_pad_nd(k4, pads, 0);
+    }
+    const int64_t blocks = (s + sparse_size - 1) / sparse_size;
+    const int64_t cols = (blocks + 31) / 32 * 32;
+    at::Tensor mask = at::empty({b, nq, blocks, cols}, query.options().dtype(at::kChar));
+    at::Tensor count = at::empty({b, nq, blocks}, query.options().dtype(at::kInt));
+    mindiesd_estimate_args a = {};
+    a.q = q4.data_ptr();
+    a.k = k4.data_ptr();
+    fill_strides(q4, head_first, a.q_stride);
+    fill_strides(k4, head_first, a.k_stride);
+    a.dtype = dtype_code(q4.scalar_type());
+    a.batch = static_cast<int32_t>(b);
+    a.heads = static_cast<int32_t>(nq);
+    a.kv_heads = static_cast<int32_t>(k4.size(ndim));
+    a.seq = static_cast<int32_t>(q4.size(sdim));
+    a.head_dim = static_cast<int32_t>(d);
+    a.stride = static_cast<int32_t>(stride);
+    a.sparse_size = static_cast<int32_t>(sparse_size);
+    a.scale = static_cast<float>(scale_value);
+    a.threshold = static_cast<float>(threshold);
+    a.row_sparse = row_sparse;
+    a.causal = 0;
+    a.keep_sink = keep_sink;
+    a.keep_recent = keep_recent;
+    a.mask = mask.data_ptr<int8_t>();
+    a.mask_cols = static_cast<int32_t>(cols);
+    a.count = count.data_ptr<int32_t>();
+    // The kernels size their rows by the padded length; the mask keeps the caller's block count.
+    TORCH_CHECK((a.seq + 127) / 128 == blocks, "sparse_block_estimate: internal block count mismatch");
+    const size_t bytes = mindiesd_sparse_block_estimate_scratch_bytes(a.batch, a.heads, a.seq);
+    at::Tensor scratch = at::empty({static_cast<int64_t>(bytes)}, query.options().dtype(at::kByte));
+    a.scratch = scratch.data_ptr();
+    a.scratch_bytes = bytes;
+    c10::cuda::CUDAGuard guard(query.device());
+    check_rc(mindiesd_sparse_block_estimate(&a, stream_of(query)), "mindiesd_sparse_block_estimate");
+    return std::make_tuple(mask, count);
+}
+
+at::Tensor ada_block_sparse_attention_cuda(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
+                                           const at::Tensor& sparse_mask, const at::Tensor& sparse_count_table,
+                                           std::string input_layout, int64_t sparse_size, int64_t num_heads,
+                                           int64_t num_key_value_heads, double scale_value, bool causal,
+                                           int64_t inner_precise, int64_t pre_tokens, int64_t next_tokens,
+                                           c10::OptionalIntArrayRef actual_seq_lengths,
+                                           c10::OptionalIntArrayRef actual_seq_lengths_kv) {
+    TORCH_CHECK(!causal, "ada_block_sparse_attention: causal=True is not supported");
+    TORCH_CHECK(sparse_size == 128, "ada_block_sparse_attention: only sparse_size=128 is supported");
+    TORCH_CHECK(!actual_seq_lengths.has_value() && !actual_seq_lengths_kv.has_value(),
+                "ada_block_sparse_attention: actual_seq_lengths are not supported");
+    TORCH_CHECK(sparse_count_table.is_cuda() && sparse_count_table.scalar_type() == at::kInt,
+                "ada_block_sparse_attention: sparse_count_table must be a CUDA int32 tensor");
+    (void)inner_precise; (void)pre_tokens; (void)next_tokens;
+    bool head_first = true, hk = true, hv = true;
+    at::Tensor out = at::empty_like(query);
+    at::Tensor q4 = view_4d(query, input_layout, num_heads, &head_first, "ada_block_sparse_attention");
+    at::Tensor k4 = view_4d(key, input_layout, num_key_value_heads, &hk, "ada_block_sparse_attention");
+    at::Tensor v4 = view_4d(value, input_layout, num_key_value_heads, &hv, "ada_block_sparse_attention");
+    at::Tensor o4 = out.dim() == 4 ? out : out.view(q4.sizes());
+    SparseSpec sp;
+    sp.mode = MINDIESD_SPARSE_MASK;
+    sp.mask = &sparse_mask;
+    run_attention(q4, k4, v4, o4, nullptr, head_first, scale_value, sp);
+    return out;
+}
+
 // ---- dense attention in the caller's layout ---------------------------------------------------------
 at::Tensor attention_fwd_cuda(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, double scale,
                               bool head_first) {
@@ -513,6 +618,16 @@ TORCH_LIBRARY(mindiesd, m) {
         "int softmax_lse_flag=0) -> (Tensor, Tensor)");
     // Operators without a counterpart schema in the reference library: there the same steps are
     // torch_npu calls or eager torch code.
+    m.def(
+        "ada_block_sparse_attention(Tensor query, Tensor key, Tensor value, Tensor sparse_mask, Tensor sparse_count_table, "
+        "str input_layout='BNSD', int sparse_size=128, int num_heads=1, int num_key_value_heads=1, float scale_value=1, "
+        "bool causal=True, int inner_precise=1, int pre_tokens=214748647, int next_tokens=0, "
+        "int[]? actual_seq_lengths=None, int[]? actual_seq_lengths_kv=None) -> Tensor");
+    m.def(
+        "sparse_block_estimate(Tensor query, Tensor key, int[]? actual_seq_lengths=None, "
+        "int[]? actual_seq_lengths_kv=None, str input_layout='BNSD', int stride=8, int sparse_size=128, "
+        "int num_heads=1, int num_key_value_heads=1, float scale_value=1, float threshold=1, bool causal=True, "
+        "bool keep_sink=True, bool keep_recent=True, float row_sparse=1) -> (Tensor, Tensor)");
     m.def("attention_fwd(Tensor query, Tensor key, Tensor value, float scale, bool head_first) -> Tensor");
     m.def("rf_rearrange(Tensor x, int[] latent_shape, int txt_len, str input_layout, bool inverse) -> Tensor");
     m.def(
@@ -533,6 +648,8 @@ TORCH_LIBRARY_IMPL(mindiesd, CUDA, m) {
     m.impl("la", &la_cuda);
     m.impl("rainfusionattention", &rainfusionattention_cuda);
     m.impl("block_sparse_attention", &block_sparse_attention_cuda);
+    m.impl("ada_block_sparse_attention", &ada_block_sparse_attention_cuda);
+    m.impl("sparse_block_estimate", &sparse_block_estimate_cuda);
     m.impl("attention_fwd", &attention_fwd_cuda);
     m.impl("rf_rearrange", &rf_rearrange_cuda);
     m.impl("rf_block_mask", &rf_block_mask_cuda);

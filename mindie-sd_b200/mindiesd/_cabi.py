@@ -104,6 +104,20 @@ class QuantArgs(C.Structure):
     ]
 
 
+class EstimateArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p),
+        ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3),
+        ("dtype", C.c_int32),
+        ("batch", C.c_int32), ("heads", C.c_int32), ("kv_heads", C.c_int32), ("seq", C.c_int32), ("head_dim", C.c_int32),
+        ("stride", C.c_int32), ("sparse_size", C.c_int32),
+        ("scale", C.c_float), ("threshold", C.c_float), ("row_sparse", C.c_double),
+        ("causal", C.c_int32), ("keep_sink", C.c_int32), ("keep_recent", C.c_int32),
+        ("mask", C.c_void_p), ("mask_cols", C.c_int32), ("count", C.c_void_p),
+        ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t),
+    ]
+
+
 def library_path() -> Path:
     override = os.environ.get("MINDIESD_B200_LIB")
     if override:
@@ -126,7 +140,8 @@ def lib():
             raise NativeLibraryError(f"cannot load {path}: {exc}") from exc
         handle.mindiesd_abi_version.restype = C.c_int
         for name in ("mindiesd_attention_fwd", "mindiesd_rf_rearrange", "mindiesd_rf_block_mask",
-                     "mindiesd_rf_pool", "mindiesd_rf_mask_from_pooled", "mindiesd_fa_block_quant"):
+                     "mindiesd_rf_pool", "mindiesd_rf_mask_from_pooled", "mindiesd_fa_block_quant",
+                     "mindiesd_sparse_block_estimate"):
             fn = getattr(handle, name, None)
             if fn is not None:
                 fn.restype = C.c_int
@@ -134,6 +149,9 @@ def lib():
         if hasattr(handle, "mindiesd_rf_block_mask_scratch_bytes"):
             handle.mindiesd_rf_block_mask_scratch_bytes.restype = C.c_size_t
             handle.mindiesd_rf_block_mask_scratch_bytes.argtypes = [C.c_int32] * 4
+        if hasattr(handle, "mindiesd_sparse_block_estimate_scratch_bytes"):
+            handle.mindiesd_sparse_block_estimate_scratch_bytes.restype = C.c_size_t
+            handle.mindiesd_sparse_block_estimate_scratch_bytes.argtypes = [C.c_int32] * 3
         handle.mindiesd_device_status.restype = C.c_int
         _lib = handle
     return _lib
@@ -322,3 +340,32 @@ def rf_block_mask_static(q, k, grid, txt_len=0, sparsity=0.0, head_first=True, p
         a.select_idx, a.select_num = sel.data_ptr(), num.data_ptr()
     check(fn(C.byref(a), current_stream_ptr(q.device)), "mindiesd_rf_block_mask_static")
     return (mask, sel, num) if want_lists else mask
+
+
+def sparse_block_estimate(q, k, scale, threshold, row_sparse=1.0, head_first=True, keep_sink=True, keep_recent=True,
+                          scratch=None):
+    """mindiesd_sparse_block_estimate on tensors whose token count is a multiple of 8.
+    Returns (int8 mask [B, N, blocks, blocks rounded up to 32], int32 count [B, N, blocks])."""
+    b, n, s, d = _dims(q, head_first)
+    nkv = k.shape[1] if head_first else k.shape[2]
+    blocks = (s + 127) // 128
+    cols = (blocks + 31) // 32 * 32
+    mask = torch.empty(b, n, blocks, cols, dtype=torch.int8, device=q.device)
+    count = torch.empty(b, n, blocks, dtype=torch.int32, device=q.device)
+    if scratch is None:
+        scratch = torch.empty(lib().mindiesd_sparse_block_estimate_scratch_bytes(b, n, s), dtype=torch.uint8,
+                              device=q.device)
+    a = EstimateArgs()
+    a.q, a.k = q.data_ptr(), k.data_ptr()
+    a.q_stride[:] = strides_bns(q, head_first)
+    a.k_stride[:] = strides_bns(k, head_first)
+    a.dtype = dtype_code(q.dtype)
+    a.batch, a.heads, a.kv_heads, a.seq, a.head_dim = b, n, nkv, s, d
+    a.stride, a.sparse_size = 8, 128
+    a.scale, a.threshold, a.row_sparse = float(scale), float(threshold), float(row_sparse)
+    a.causal, a.keep_sink, a.keep_recent = 0, int(keep_sink), int(keep_recent)
+    a.mask, a.mask_cols, a.count = mask.data_ptr(), cols, count.data_ptr()
+    a.scratch, a.scratch_bytes = scratch.data_ptr(), scratch.numel()
+    check(lib().mindiesd_sparse_block_estimate(C.byref(a), current_stream_ptr(q.device)),
+          "mindiesd_sparse_block_estimate")
+    return mask, count

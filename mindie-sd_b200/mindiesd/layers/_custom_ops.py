@@ -1,7 +1,7 @@
 """Keyword wrappers around torch.ops.mindiesd.* and their fake implementations.
 
-The three attention wrappers keep the names, argument names and defaults of
-mindiesd/layers/_custom_ops.py:19-72, 124-189, 330-390 of MindIE-SD.
+The attention and estimator wrappers keep the names, argument names and defaults of
+mindiesd/layers/_custom_ops.py:19-72, 124-390 of MindIE-SD.
 """
 from __future__ import annotations
 
@@ -10,6 +10,7 @@ from typing import List, Optional, Tuple
 import torch
 
 from . import register_ops
+from ..utils.exception import ParametersInvalid
 
 
 def laser_attention(query, key, value, atten_mask=None, alibi_mask=None, drop_mask=None, scale_value=1.0,
@@ -74,6 +75,57 @@ def _block_sparse_fake(query, key, value, block_sparse_mask=None, block_shape=No
     else:
         shape = [query.shape[0], query.shape[1], query.shape[2], 1]
     return torch.empty_like(query), query.new_empty(shape, dtype=torch.float32)
+
+
+def sparse_block_estimate(query, key, actual_seq_lengths: Optional[List[int]] = None,
+                          actual_seq_lengths_kv: Optional[List[int]] = None, input_layout="BNSD", stride=8,
+                          sparse_size=128, num_heads=1, num_key_value_heads=1, scale_value=1.0, threshold=1.0,
+                          causal=False, keep_sink=True, keep_recent=True,
+                          row_sparse=1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    return torch.ops.mindiesd.sparse_block_estimate(
+        query=query, key=key, actual_seq_lengths=actual_seq_lengths, actual_seq_lengths_kv=actual_seq_lengths_kv,
+        input_layout=input_layout, stride=stride, sparse_size=sparse_size, num_heads=num_heads,
+        num_key_value_heads=num_key_value_heads, scale_value=scale_value, threshold=threshold, causal=causal,
+        keep_sink=keep_sink, keep_recent=keep_recent, row_sparse=row_sparse)
+
+
+@register_ops.register_mindie_fake_op("sparse_block_estimate")
+def _sparse_block_estimate_fake(query, key, actual_seq_lengths=None, actual_seq_lengths_kv=None, input_layout="BNSD",
+                                stride=8, sparse_size=128, num_heads=1, num_key_value_heads=1, scale_value=1.0,
+                                threshold=1.0, causal=False, keep_sink=True, keep_recent=True, row_sparse=1.0):
+    if input_layout == "BNSD":
+        b, nq, s, _ = query.shape
+    elif input_layout == "BSND":
+        b, s, nq, _ = query.shape
+    elif input_layout == "BSH":
+        b, s, _ = query.shape
+        nq = num_heads
+    else:
+        raise ParametersInvalid(f"The input_layout only support 'BNSD', 'BSND' and 'BSH', but got {input_layout}")
+    blocks = (s + sparse_size - 1) // sparse_size
+    mask = query.new_empty([b, nq, blocks, (blocks + 31) // 32 * 32], dtype=torch.int8)
+    return mask, query.new_empty([b, nq, blocks], dtype=torch.int32)
+
+
+def ada_block_sparse_attention(query, key, value, sparse_mask, sparse_count_table, input_layout="BNSD",
+                               sparse_size=128, num_heads=1, num_key_value_heads=1, scale_value=1.0, causal=False,
+                               inner_precise=1, pre_tokens=214748647, next_tokens=214748647,
+                               actual_seq_lengths: Optional[List[int]] = None,
+                               actual_seq_lengths_kv: Optional[List[int]] = None) -> torch.Tensor:
+    return torch.ops.mindiesd.ada_block_sparse_attention(
+        query=query, key=key, value=value, sparse_mask=sparse_mask, sparse_count_table=sparse_count_table,
+        input_layout=input_layout, sparse_size=sparse_size, num_heads=num_heads,
+        num_key_value_heads=num_key_value_heads, scale_value=scale_value, causal=causal,
+        inner_precise=inner_precise, pre_tokens=pre_tokens, next_tokens=next_tokens,
+        actual_seq_lengths=actual_seq_lengths, actual_seq_lengths_kv=actual_seq_lengths_kv)
+
+
+@register_ops.register_mindie_fake_op("ada_block_sparse_attention")
+def _ada_block_sparse_attention_fake(query, key, value, sparse_mask, sparse_count_table, input_layout="BNSD",
+                                     sparse_size=128, num_heads=1, num_key_value_heads=1, scale_value=1.0,
+                                     causal=False, inner_precise=1, pre_tokens=214748647, next_tokens=214748647,
+                                     actual_seq_lengths=None, actual_seq_lengths_kv=None):
+    return torch.empty_like(query)
 
 
 # ---- operators that replace torch_npu calls or eager torch code of the reference ---------------------

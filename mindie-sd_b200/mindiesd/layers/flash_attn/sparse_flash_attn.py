@@ -4,6 +4,7 @@ from typing import Optional
 
 import torch
 
+from .sparse_flash_attn_ada_bsa import ada_block_sparse_attention, get_estimate_mask
 from .sparse_flash_attn_rf_v2 import rain_fusion_attention
 from .sparse_flash_attn_rf_v3 import bsa_sparse_attention_v3, do_tensor_rearrange_only
 from ...utils.exception import ParametersInvalid
@@ -54,7 +55,11 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attn_mas
                                          input_layout=input_layout, head_num=head_num, scale=scale,
                                          inner_precise=inner_precise)
     elif sparse_type == "ada_bsa":
-        raise ParametersInvalid("sparse_type 'ada_bsa' (CDF-threshold block estimation) is not part of this build.")
+        smask, sct = get_estimate_mask(q, k, v, scale=scale, head_num=head_num, is_causal=is_causal,
+                                       input_layout=input_layout, keep_sink=keep_sink, keep_recent=keep_recent,
+                                       sparsity=sparsity, cdf_threshold=cdf_threshold, sparse_size=block_size)
+        out = ada_block_sparse_attention(q, k, v, smask, sct, scale=scale, head_num=head_num, is_causal=is_causal,
+                                         input_layout=input_layout, sparse_size=block_size)
     else:
         out = torch.ops.mindiesd.attention_fwd(q, k, v, float(scale), input_layout == "BNSD")
     return out

@@ -41,3 +41,11 @@ MASK_CASES = [
 ]
 
 PERM_GRIDS = [(3, 40, 80), (3, 30, 52), (2, 21, 32), (2, 24, 45), (4, 8, 16), (3, 12, 11), (2, 9, 16)]
+
+# (name, grid, heads, cdf threshold, row_sparse, seed): sequence = t*h*w tokens
+ESTIMATE_CASES = [
+    ("aligned", (2, 32, 32), 2, 0.85, 1.0, 51),      # 2048 tokens, 16 blocks
+    ("ragged_block", (1, 29, 40), 2, 0.7, 1.0, 52),  # 1160 tokens: a multiple of 8, not of 128
+    ("ragged_group", (1, 13, 89), 1, 0.9, 0.5, 53),  # 1157 tokens: not a multiple of 8; row cap active
+    ("two_chunks", (3, 60, 52), 1, 0.6, 1.0, 54),    # 9360 tokens: more than one 8192-token key chunk of the golden
+]

@@ -5,8 +5,9 @@
 The reference is imported with `torch_npu` replaced by a mock, exactly as its own CPU test runner
 does (tests/run.py:29-41 of MindIE-SD); only its pure-torch functions are called:
 attention_forward(fused=False), avgpool, rearrange_with_remaining, inv_rearrange_with_remaining,
-do_tensor_rearrange_pooling, get_blockwise_mask, get_mask_index, and the numpy block-sparse golden
-of tests/plugin/test_block_sparse_attention.py.  Masks are stored bit-packed.
+do_tensor_rearrange_pooling, get_blockwise_mask, get_mask_index, and the numpy goldens of its plugin tests
+(tests/plugin/test_block_sparse_attention.py, test_sparseblockestimate.py,
+test_adablocksparseattention.py).  Masks are stored bit-packed.
 """
 import importlib.util
 import os
@@ -36,15 +37,17 @@ def import_reference(root):
     import mindiesd  # noqa: F401
     from mindiesd.layers.flash_attn import sparse_flash_attn_rf_v2 as rf
     from mindiesd.layers.flash_attn.attention_forward import attention_forward
-    spec = importlib.util.spec_from_file_location(
-        "ref_bsa_test", os.path.join(root, "tests", "plugin", "test_block_sparse_attention.py"))
-    bsa = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(bsa)
-    return rf, attention_forward, bsa
+    mods = []
+    for name in ("test_block_sparse_attention", "test_sparseblockestimate", "test_adablocksparseattention"):
+        spec = importlib.util.spec_from_file_location("ref_" + name, os.path.join(root, "tests", "plugin", name + ".py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mods.append(mod)
+    return rf, attention_forward, mods
 
 
 def main(root):
-    rf, attention_forward, bsa = import_reference(root)
+    rf, attention_forward, (bsa, est, ada) = import_reference(root)
     torch.set_num_threads(8)
 
     # 1. permutations: the reference applied to a tensor whose value is its own token index
@@ -122,6 +125,25 @@ def main(root):
     mask[0, 0, 1, :] = 0  # a row that keeps nothing
     o = bsa.block_sparse_attention_cpu(q, k, v, mask, 128)
     np.savez_compressed(HERE / "block_sparse.npz", mask=mask.numpy(), out=o.numpy())
+
+    # 7. ada_bsa: the estimator's numpy golden on structured inputs (bf16 values, fp32 arithmetic)
+    out = {}
+    for (name, grid, heads, threshold, row_sparse, seed) in inputs.ESTIMATE_CASES:
+        q, k = inputs.structured_qk(seed, heads, grid, 128)
+        q, k = q.float().numpy(), k.float().numpy()
+        m = est.sparse_estimate_cpu(q, k, False, blocksize=128, stride=8, threshold=threshold, force_sparse=row_sparse)
+        out[f"{name}_shape"] = np.array(m.shape, dtype=np.int32)
+        out[f"{name}_bits"] = np.packbits(m.reshape(-1))
+        print(name, m.shape, "density %.4f" % m.mean())
+    np.savez_compressed(HERE / "estimate.npz", **out)
+
+    # 8. ada_bsa: the attention golden (mask columns padded to a multiple of 32, as the operator takes them)
+    q, k, v = (inputs.randn(41 + i, 1, 2, 300, 128, dtype=torch.bfloat16) for i in range(3))
+    mask = torch.zeros(1, 2, 3, 32, dtype=torch.int8)
+    mask[..., :3] = torch.from_numpy((np.random.RandomState(44).rand(1, 2, 3, 3) < 0.6).astype(np.int8))
+    mask[0, 1, 2, :] = 0  # a row that keeps nothing
+    o = ada.ada_block_sparse_attention_cpu(q, k, v, mask, causal=False, blocksize=128)
+    np.savez_compressed(HERE / "ada_attention.npz", mask=mask.numpy(), out=o.numpy())
 
 
 if __name__ == "__main__":

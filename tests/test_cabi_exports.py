@@ -37,7 +37,8 @@ def test_struct_layouts_match_the_header(tmp_path):
         pytest.skip("no C compiler")
     structs = {"mindiesd_attn_args": _cabi.AttnArgs, "mindiesd_rearrange_args": _cabi.RearrangeArgs,
                "mindiesd_mask_args": _cabi.MaskArgs, "mindiesd_pool_args": _cabi.PoolArgs,
-               "mindiesd_pooled_mask_args": _cabi.PooledMaskArgs, "mindiesd_quant_args": _cabi.QuantArgs}
+               "mindiesd_pooled_mask_args": _cabi.PooledMaskArgs, "mindiesd_quant_args": _cabi.QuantArgs,
+               "mindiesd_estimate_args": _cabi.EstimateArgs}
     src = tmp_path / "sz.c"
     body = "".join(f'printf("{n} %zu\\n", sizeof({n}));' for n in structs)
     src.write_text(f'#include <stdio.h>\n#include "mindiesd_b200.h"\nint main(void){{{body}return 0;}}\n')
@@ -63,6 +64,16 @@ def test_invalid_arguments_return_codes_without_a_gpu():
     assert lib.mindiesd_rf_rearrange(ctypes.byref(r), None) == -1
     q = _cabi.QuantArgs()
     assert lib.mindiesd_fa_block_quant(ctypes.byref(q), None) == -1
+    e = _cabi.EstimateArgs()
+    assert lib.mindiesd_sparse_block_estimate(ctypes.byref(e), None) == -1
+    e.q = e.k = e.mask = e.count = e.scratch = 4096
+    e.batch = e.heads = e.kv_heads = 1
+    e.head_dim, e.stride, e.sparse_size, e.scale, e.threshold = 128, 8, 128, 0.01, 0.9
+    e.seq = 1001
+    assert lib.mindiesd_sparse_block_estimate(ctypes.byref(e), None) == -2  # not a multiple of 8 tokens
+    e.seq, e.causal = 1024, 1
+    assert lib.mindiesd_sparse_block_estimate(ctypes.byref(e), None) == -5  # causal is not supported
+    assert lib.mindiesd_sparse_block_estimate_scratch_bytes(1, 40, 75600) == 4 * 9472 * (37 * 16 + 37) * 4
     with pytest.raises(_cabi.NativeLibraryError):
         _cabi.check(-2, "x")
 
@@ -74,5 +85,9 @@ def test_operator_library_registers_reference_schemas():
     assert "Tensor? atten_mask=None" in la and "bool is_highPrecision=True" in la and "int next_tokens=1" in la
     bsa = str(torch.ops.mindiesd.block_sparse_attention.default._schema)
     assert "int[] block_shape=" in bsa and "int softmax_lse_flag=0" in bsa and "int num_key_value_heads=1" in bsa
+    est = str(torch.ops.mindiesd.sparse_block_estimate.default._schema)
+    assert "int[]? actual_seq_lengths=None" in est and "bool keep_recent=True" in est and "float row_sparse=1" in est
+    ada = str(torch.ops.mindiesd.ada_block_sparse_attention.default._schema)
+    assert "Tensor sparse_count_table" in ada and "int pre_tokens=214748647" in ada and "-> Tensor" in ada
     rf = str(torch.ops.mindiesd.rainfusionattention.default._schema)
     assert "Tensor select_num_idx" in rf and "str q_input_layout=\"TND\"" in rf and "int inner_precise=1" in rf

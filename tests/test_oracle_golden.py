@@ -7,6 +7,7 @@ import pytest
 import torch
 
 import inputs
+from oracle import ada_bsa as oada
 from oracle import attention as oa
 from oracle import rainfusion as orf
 
@@ -118,6 +119,36 @@ def test_block_sparse_attention_matches_reference():
     assert (got - want).abs().max().item() < 1e-6
     assert torch.count_nonzero(want[0, 0, 128:256]) == 0  # the row that keeps nothing
     assert oa.ref_compare(want, got, 2 ** -6)[1]
+
+
+def test_sparse_block_estimate_matches_reference():
+    """The restated estimator against the reference's numpy golden, bit for bit (the golden's mixed
+    float64 / float32 comparison included), and the single-precision decision against it: the two
+    may differ in one block per row, the one whose score is the row's guard."""
+    z = np.load(G / "estimate.npz")
+    for (name, grid, heads, threshold, row_sparse, seed) in inputs.ESTIMATE_CASES:
+        q, k = inputs.structured_qk(seed, heads, grid, 128)
+        q, k = q.float().numpy(), k.float().numpy()
+        shape = tuple(z[f"{name}_shape"])
+        want = np.unpackbits(z[f"{name}_bits"])[:int(np.prod(shape))].reshape(shape).astype(bool)
+        got, count, score = oada.sparse_block_estimate(q, k, 128 ** -0.5 / 8, threshold, row_sparse,
+                                                       golden_rounding=True)
+        assert np.array_equal(got, want), (name, int((got != want).sum()))
+        assert np.array_equal(count, got.sum(-1)), name
+        assert got[..., 0].all() and got[..., -1].all(), name
+        assert np.allclose(score.sum(-1)[..., :-1], 16.0, atol=1e-9), name  # 16 rows of softmax mass per block
+        plain, _, _ = oada.sparse_block_estimate(q, k, 128 ** -0.5 / 8, threshold, row_sparse)
+        assert not (want & ~plain).any(), name
+        assert (plain & ~want).sum(-1).max() <= 1, name
+
+
+def test_ada_attention_golden_is_the_block_sparse_golden():
+    z = np.load(G / "ada_attention.npz")
+    q, k, v = (inputs.randn(41 + i, 1, 2, 300, 128, dtype=torch.bfloat16) for i in range(3))
+    got = oa.block_sparse_attention(q, k, v, z["mask"], 128)
+    want = torch.from_numpy(z["out"])
+    assert (got - want).abs().max().item() < 1e-6
+    assert torch.count_nonzero(want[0, 1, 256:]) == 0  # the row that keeps nothing
 
 
 def test_temporal_band_extension():
