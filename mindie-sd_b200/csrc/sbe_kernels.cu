@@ -17,8 +17,8 @@
 //   warps 0-3  softmax (one query group per thread)   warp 4  MMA issue   warp 5  TMA loads
 //
 // Kernel 2 (sbe_select_kernel): one CTA per (query block, head): rescales and normalises the 16
-// rows, adds them, sorts the block scores (bitonic, shared memory), scans them and writes the int8
-// mask row and the kept count.
+// rows, adds them, finds the guard score of the cumulative-mass rule by a bitwise search (no sort)
+// and writes the int8 mask row and the kept count.
 #include "capi_common.h"
 #include "fa_fwd.h"
 #include "ptx_sm100.cuh"
@@ -293,14 +293,16 @@ struct SelectParams {
     int32_t* count; // [batch][heads][blocks]
 };
 
-constexpr int kThreads2 = 256;
+constexpr int kThreads2 = 128;
 
+// kPerLane: ceil(blocks / 32) rounded up to a supported size; warp 0 holds the row's scores in
+// registers during the search.
+template <int kPerLane>
 __global__ void __launch_bounds__(kThreads2) sbe_select_kernel(const SelectParams p) {
     __shared__ float factor[kBlockGroups][kMaxTrips];  // 2^(m_used - m_final) / row sum
     __shared__ float score[kMaxMaskBlocks];
-    __shared__ float sorted[kMaxMaskBlocks];
-    __shared__ float scan[kThreads2];
     __shared__ float row_sum[kBlockGroups];
+    __shared__ uint32_t guard_smem;
     __shared__ int count_smem;
     const int qb = blockIdx.x;
     const int pair = p.pair0 + blockIdx.y;
@@ -318,8 +320,9 @@ __global__ void __launch_bounds__(kThreads2) sbe_select_kernel(const SelectParam
         }
         factor[r][t] = f;
     }
+    if (tid == 0) count_smem = 0;
     __syncthreads();
-    // Row sums: the softmax denominator in units of the final maximum.  Two rows per warp.
+    // Row sums: the softmax denominator in units of the final maximum.  Four rows per warp.
     for (int r = warp; r < kBlockGroups; r += kThreads2 / 32) {
         float s = 0.f;
         if (r < nrows) {
@@ -336,83 +339,59 @@ __global__ void __launch_bounds__(kThreads2) sbe_select_kernel(const SelectParam
         if (r < nrows) factor[r][t] = factor[r][t] / row_sum[r];
     }
     __syncthreads();
-    // Padded length of the sort: the next power of two.
-    int n2 = 32;
-    while (n2 < p.blocks) n2 <<= 1;
-    for (int j = tid; j < n2; j += kThreads2) {
+    for (int j = tid; j < p.blocks; j += kThreads2) {
+        const int t = j / kTripBlocks;
         float s = 0.f;
-        if (j < p.blocks) {
-            const int t = j / kTripBlocks;
-            for (int r = 0; r < nrows; ++r) s += p.partial[(row_base + r) * cols + j] * factor[r][t];
-            if (p.keep_recent && j == p.blocks - 1) s = 0.f;  // the last block is kept anyway and does not compete
-        }
+        for (int r = 0; r < nrows; ++r) s += p.partial[(row_base + r) * cols + j] * factor[r][t];
+        if (p.keep_recent && j == p.blocks - 1) s = 0.f;  // the last block is kept anyway and does not compete
         score[j] = s;
-        sorted[j] = j < p.blocks ? s : -1.f;  // padding sorts behind every score (scores are >= 0)
     }
     __syncthreads();
-    // Bitonic sort, descending.
-    for (int k = 2; k <= n2; k <<= 1) {
-        for (int j = k >> 1; j > 0; j >>= 1) {
-            for (int i = tid; i < n2; i += kThreads2) {
-                const int partner = i ^ j;
-                if (partner > i) {
-                    const float a = sorted[i], b = sorted[partner];
-                    const bool descending = (i & k) == 0;
-                    if (descending ? (a < b) : (a > b)) {
-                        sorted[i] = b;
-                        sorted[partner] = a;
-                    }
-                }
-            }
-            __syncthreads();
-        }
-    }
-    // Inclusive prefix sums of the sorted scores: a contiguous segment per thread, then a scan of the
-    // segment totals.
-    const int seg = n2 / kThreads2 > 0 ? n2 / kThreads2 : 1;
-    const int first = tid * seg;
-    float local = 0.f;
-    if (first < n2)
-        for (int i = 0; i < seg; ++i) local += fmaxf(sorted[first + i], 0.f);
-    scan[tid] = local;
-    __syncthreads();
-    for (int o = 1; o < kThreads2; o <<= 1) {
-        const float add = tid >= o ? scan[tid - o] : 0.f;
-        __syncthreads();
-        scan[tid] += add;
-        __syncthreads();
-    }
-    const float total = scan[kThreads2 - 1];
-    const float limit = p.threshold * total;
-    if (tid == 0) count_smem = 0;
-    __syncthreads();
-    int below = 0;
-    if (first < n2) {
-        float run = scan[tid] - local;
-        for (int i = 0; i < seg; ++i) {
-            if (first + i < p.blocks) {
-                run += sorted[first + i];
-                below += run < limit;
-            }
-        }
-    }
+    // The guard is the score of the block at which the running sum of the descending scores first reaches
+    // `threshold` of the total: the largest score v for which the blocks scoring at least v hold that
+    // much -- or, if that takes more than max_keep blocks, the max_keep-th largest score.  Both
+    // conditions are monotone in v, so the guard is found bit by bit on the scores' bit patterns
+    // (non-negative floats order like unsigned integers) without sorting.
+    if (warp == 0) {
+        float x[kPerLane];
+        float total = 0.f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) below += __shfl_xor_sync(0xffffffffu, below, o);
-    if (lane == 0 && below) atomicAdd(&count_smem, below);
+        for (int i = 0; i < kPerLane; ++i) {
+            const int j = lane + 32 * i;
+            x[i] = j < p.blocks ? score[j] : -1.f;  // padding never reaches a candidate
+            total += fmaxf(x[i], 0.f);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        const float limit = p.threshold * total;
+        uint32_t thr = 0;
+        if (total > 0.f) {
+            for (int bit = 30; bit >= 0; --bit) {
+                const uint32_t cand = thr | (1u << bit);
+                float mass = 0.f;
+                int cnt = 0;
+#pragma unroll
+                for (int i = 0; i < kPerLane; ++i) {
+                    const bool ge = x[i] >= 0.f && __float_as_uint(x[i]) >= cand;
+                    mass += ge ? x[i] : 0.f;
+                    cnt += ge;
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) mass += __shfl_xor_sync(0xffffffffu, mass, o);
+                cnt = __reduce_add_sync(0xffffffffu, cnt);
+                if (mass >= limit || cnt >= p.max_keep) thr = cand;
+            }
+        }
+        if (lane == 0) guard_smem = thr;
+    }
     __syncthreads();
-    int cnt = count_smem + 1;
-    if (cnt > p.max_keep) cnt = p.max_keep;
-    cnt = max(1, min(cnt, p.blocks));
-    const float guard = sorted[cnt - 1];
-    __syncthreads();
-    if (tid == 0) count_smem = 0;
-    __syncthreads();
+    const uint32_t guard = guard_smem;
     int8_t* mrow = p.mask + (static_cast<int64_t>(pair) * p.blocks + qb) * p.mask_cols;
     int kept = 0;
     for (int j = tid; j < p.mask_cols; j += kThreads2) {
         bool keep = false;
         if (j < p.blocks)
-            keep = score[j] >= guard || (p.keep_sink && j == 0) || (p.keep_recent && j == p.blocks - 1);
+            keep = __float_as_uint(score[j]) >= guard || (p.keep_sink && j == 0) || (p.keep_recent && j == p.blocks - 1);
         mrow[j] = keep ? 1 : 0;
         kept += keep;
     }
@@ -555,7 +534,12 @@ extern "C" int mindiesd_sparse_block_estimate(const mindiesd_estimate_args* a, v
         p.pair0 = sp.pair0 = static_cast<int>(pair0);
         kernel<<<dim3(s.groups_pad / kRows, n), kThreads1, kSmem1, stream>>>(p);
         if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
-        sbe_select_kernel<<<dim3(s.blocks, n), kThreads2, 0, stream>>>(sp);
+        const dim3 grid2(s.blocks, n);
+        const int per_lane = (s.blocks + 31) / 32;
+        if (per_lane <= 8) sbe_select_kernel<8><<<grid2, kThreads2, 0, stream>>>(sp);
+        else if (per_lane <= 20) sbe_select_kernel<20><<<grid2, kThreads2, 0, stream>>>(sp);
+        else if (per_lane <= 32) sbe_select_kernel<32><<<grid2, kThreads2, 0, stream>>>(sp);
+        else sbe_select_kernel<64><<<grid2, kThreads2, 0, stream>>>(sp);
         if ((e = cudaGetLastError()) != cudaSuccess) return static_cast<int>(e);
     }
     return MINDIESD_OK;
