@@ -3,8 +3,9 @@ ABI and through torch.ops.mindiesd.sparse_block_estimate) and the attention over
 
 The estimator's decision is a threshold on floating-point sums, so parity is stated as the
 reference's own plugin test states it (tests/plugin/test_sparseblockestimate.py:225-239: fewer than
-2 % of the selected blocks differ, fewer than 1 % are omitted) and, more strictly, as: every bit that
-differs from the oracle belongs to a block whose score is within 1e-3 of its row's guard value."""
+2 % of the selected blocks differ, fewer than 1 % are omitted) and, more strictly, as: every row that
+differs from the oracle's is a correct decision up to rounding (a score within 1e-3 of the row's
+guard, or a running sum within 1e-5 of the limit), and at most 1 % of the kept blocks differ."""
 from pathlib import Path
 
 import numpy as np
