@@ -226,7 +226,8 @@ def dense_or_ulysses(args, rank, world, device):
         hq, hk, hv = (torch.empty(x.shape, dtype=x.dtype, pin_memory=True).copy_(x) for x in (q, k, v))
     ho = torch.empty(hq.shape, dtype=q.dtype, pin_memory=True)
     from mindiesd import attention_forward_host
-    e2e_chunks = 5 if cfg.heads % 5 == 0 else 1
+    from mindiesd.layers.flash_attn.host_io import default_host_chunks
+    e2e_chunks = args.e2e_chunks if args.e2e_chunks and cfg.heads % args.e2e_chunks == 0 else default_host_chunks(cfg.heads, cfg.seq)
 
     def e2e_step():
         if world == 1:
@@ -408,6 +409,7 @@ def main():
     ap.add_argument("--workload", default="dense")
     ap.add_argument("--sparsity", type=float, default=0.75)
     ap.add_argument("--band", type=int, default=-1)
+    ap.add_argument("--e2e-chunks", type=int, default=0, help="head chunks of the pipelined end-to-end leg (0: the API's default)")
     ap.add_argument("--cdf", type=float, default=0.9, help="cumulative-mass threshold of the ada_bsa estimate")
     ap.add_argument("--heads", type=int, default=0, help="reduced head count for profiler captures (default: the full 40)")
     ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs (profiler captures)")

@@ -62,3 +62,11 @@ def test_block_mask_cache_hands_the_kept_mask_back():
             assert cached is None  # the builder runs
         else:
             assert cached == f"mask{(step - step % 3, block)}"
+
+
+def test_default_host_chunks():
+    from mindiesd.layers.flash_attn.host_io import default_host_chunks
+    assert default_host_chunks(40, 75600) == 40   # one head per chunk still launches two waves
+    assert default_host_chunks(12, 32760) == 4    # 128 thread blocks per head: three heads per chunk
+    assert default_host_chunks(2, 300) == 1
+    assert default_host_chunks(7, 1 << 20) == 7

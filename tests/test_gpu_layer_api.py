@@ -184,10 +184,12 @@ def test_attention_forward_host_pipeline():
     from mindiesd import attention_forward_host, ParametersInvalid
     q, k, v = (inputs.randn(210 + i, 1, 6, 700, 128, dtype=torch.bfloat16).pin_memory() for i in range(3))
     want = oa.attention_math(q, k, v, head_first=True)
-    for chunks in (1, 3):
+    for chunks in (1, 3, 6, None, 3):  # 6: more chunks than staging slots; None: the default; 3 again: buffers re-made
         out = attention_forward_host(q, k, v, head_chunks=chunks)
         assert out.is_pinned() and not out.is_cuda
         _close(out, want)
+    first = attention_forward_host(q, k, v, head_chunks=6).clone()
+    assert torch.equal(attention_forward_host(q, k, v, head_chunks=6), first)  # staging reuse across calls
     with pytest.raises(ParametersInvalid):
         attention_forward_host(q, k, v, head_chunks=4)
     with pytest.raises(ParametersInvalid):
