@@ -98,5 +98,7 @@ def attention_forward_host(query: torch.Tensor, key: torch.Tensor, value: torch.
             out[:, c * hc:(c + 1) * hc].copy_(do, non_blocking=True)
             stored[c] = torch.cuda.Event()
             stored[c].record(copy_out)
+    # The calling stream is ordered after the last copy out, and so is the host.
+    compute.wait_event(stored[head_chunks - 1])
     stored[head_chunks - 1].synchronize()
     return out

@@ -178,6 +178,10 @@ def test_ops_trace_with_fake_tensors():
         assert out.shape == q.shape and lse.shape == (1, 2, 1024, 1)
         lse, out = torch.ops.mindiesd.la(q, q, q)
         assert out.dtype == torch.float32
+        smask, sct = torch.ops.mindiesd.sparse_block_estimate(q, q, causal=False)
+        assert smask.shape == (1, 2, 8, 32) and smask.dtype == torch.int8 and sct.shape == (1, 2, 8)
+        out = torch.ops.mindiesd.ada_block_sparse_attention(q, q, q, smask, sct, causal=False)
+        assert out.shape == q.shape and out.dtype == q.dtype
 
 
 def test_attention_forward_host_pipeline():
