@@ -348,6 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         // The running max may lag the true max by this much (log2 units) before O is rescaled; the
         // probabilities then reach 2^lag, which two-byte formats hold but e4m3 does not.
         constexpr float kLag = kFp8 ? kFp8Lag : kRescaleThreshold;
+        constexpr float kRedoSum = 256.0f;  // 2^kRescaleThreshold
 
         // e4m3: the dequantisation scales of the q block and of each k block fold into the
         // exponent's multiplier; a per-token-block v scale folds into the exponent's offset.
@@ -403,37 +404,46 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                         if (c * 32 + i >= tail_valid) s[c][i] = 0xff800000u;  // -inf
             }
             auto row_max = [&]() {
-                // Eight independent chains: a single running max would be 128 dependent instructions.
+                // Eight independent chains of three-input max: a single running max would be 128 dependent
+                // instructions.
                 float mx8[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(__uint_as_float(s[0][i]), __uint_as_float(s[0][i + 8]));
+                for (int i = 0; i < 8; ++i)
+                    mx8[i] = fmax3(__uint_as_float(s[0][i]), __uint_as_float(s[0][i + 8]), __uint_as_float(s[0][i + 16]));
 #pragma unroll
-                for (int i = 16; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(s[0][i]));
+                for (int i = 0; i < 8; ++i) mx8[i] = fmax3(mx8[i], __uint_as_float(s[0][i + 24]), __uint_as_float(s[1][i]));
 #pragma unroll
-                for (int c = 1; c < 4; ++c)
+                for (int i = 0; i < 8; ++i) mx8[i] = fmax3(mx8[i], __uint_as_float(s[1][i + 8]), __uint_as_float(s[1][i + 16]));
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(s[c][i]));
-                return fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+                for (int i = 0; i < 8; ++i) mx8[i] = fmax3(mx8[i], __uint_as_float(s[1][i + 24]), __uint_as_float(s[2][i]));
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mx8[i] = fmax3(mx8[i], __uint_as_float(s[2][i + 8]), __uint_as_float(s[2][i + 16]));
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mx8[i] = fmax3(mx8[i], __uint_as_float(s[2][i + 24]), __uint_as_float(s[3][i]));
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mx8[i] = fmax3(mx8[i], __uint_as_float(s[3][i + 8]), __uint_as_float(s[3][i + 16]));
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(mx8[i], __uint_as_float(s[3][i + 24]));
+                return fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             };
             if constexpr (!kFp8) {
-                // The probabilities are computed against the running max right away; the block's own max
-                // is found alongside (it does not touch the exponent unit) and only if it exceeds the
-                // running max by more than the allowed lag -- rare after the first blocks -- is the block
-                // redone.  This keeps the max off the critical path.  The first block has no running max
-                // yet and takes its own first.
-                float alpha_total = 1.0f;
+                // The probabilities are taken against the running max right away and kept in registers; the
+                // scores die as they are consumed.  Every probability is non-negative, so a row sum within
+                // 2^lag bounds each of them: only if that test fails somewhere in the warp -- rare after the
+                // first blocks -- are the scores fetched again (nothing has been stored over them yet), the
+                // block's own max taken, O and the running sum rescaled, and the probabilities redone.  The
+                // first block has no running max yet and takes its own first.
                 if (cnt == 0) m_run = row_max() * mult;
                 const uint64_t mult2 = pack2(mult, mult);
+                uint32_t pk[4][16];
                 float sum = 0.0f;
     #pragma unroll 1
                 for (int pass = 0; pass < 2; ++pass) {
-                    const float neg_m = kFp8 ? (kFp8PShiftLog2 + v_off - m_run) : -m_run;
+                    const float neg_m = -m_run;
                     const uint64_t negm2 = pack2(neg_m, neg_m);
                     uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
     #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        uint32_t pk[kFp8 ? 8 : 16];
     #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             float e0, e1, e2, e3;
@@ -445,15 +455,9 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                             e3 = ex2_approx(e3);
                             sum2[0] = add2(sum2[0], pack2(e0, e1));
                             sum2[1] = add2(sum2[1], pack2(e2, e3));
-                            if constexpr (kFp8) {
-                                pk[i] = pack_quad_e4m3(e0, e1, e2, e3);
-                            } else {
-                                pk[2 * i] = pack_pair(e0, e1, kIn);
-                                pk[2 * i + 1] = pack_pair(e2, e3, kIn);
-                            }
+                            pk[c][2 * i] = pack_pair(e0, e1, kIn);
+                            pk[c][2 * i + 1] = pack_pair(e2, e3, kIn);
                         }
-                        if constexpr (kFp8) tmem_st8(taddr_s + c * 8, pk);
-                        else tmem_st16(taddr_s + c * 16, pk);
                     }
                     {
                         float a, b;
@@ -461,27 +465,36 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                         sum = a + b;
                     }
                     if (pass == 1 || cnt == 0) break;
-                    const float m_cand = row_max() * mult;
-                    if (!__any_sync(0xffffffffu, m_cand > m_run + kLag)) break;
-                    const float m_new = fmaxf(m_run, m_cand);
-                    alpha_total = ex2_approx(m_run - m_new);
-                    m_run = m_new;
-                }
-                const bool rescale = alpha_total != 1.0f;  // per thread; the warp-wide decision follows
-                l_run *= alpha_total;
-                // The scores are dead now; the (rare) rescale of O reuses their registers.
-                if (cnt > 0 && __any_sync(0xffffffffu, rescale)) {
+                    if (!__any_sync(0xffffffffu, !(sum <= kRedoSum))) break;
     #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t o[32];
-                        tmem_ld32(taddr_o + c * 32, o);
+                    for (int c = 0; c < 4; ++c) tmem_ld32(taddr_s + c * 32, s[c]);
+                    tmem_wait_ld();
+                    if (tail) {
+    #pragma unroll
+                        for (int c = 0; c < 4; ++c)
+    #pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (c * 32 + i >= tail_valid) s[c][i] = 0xff800000u;  // -inf
+                    }
+                    const float m_new = fmaxf(m_run, row_max() * mult);
+                    const float alpha = ex2_approx(m_run - m_new);
+                    m_run = m_new;
+                    l_run *= alpha;
+                    // The previous P V product has finished (the scores were issued behind it) and this
+                    // block's has not been handed over: O is at rest.
+    #pragma unroll 1
+                    for (int c = 0; c < kHeadDim / 8; ++c) {
+                        uint32_t o[8];
+                        tmem_ld8(taddr_o + c * 8, o);
                         tmem_wait_ld();
     #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha_total);
-                        tmem_st32(taddr_o + c * 32, o);
+                        for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st8(taddr_o + c * 8, o);
                     }
                 }
-                l_run += sum * l_fix;
+    #pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_st16(taddr_s + c * 16, pk[c]);
+                l_run += sum;
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(bar_p(t, 1));
