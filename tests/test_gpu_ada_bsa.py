@@ -174,3 +174,18 @@ def test_sparse_attention_ada_bsa_end_to_end(layout):
     want = oa.block_sparse_attention(q, k, v, smask.cpu().numpy(), 128)
     got = out.cpu().float() if layout == "BNSD" else out.cpu().float().transpose(1, 2)
     assert (got - want).abs().max().item() < 2e-2 and (got - want).abs().mean().item() < 2e-3
+
+
+def test_full_threshold_is_dense_attention():
+    """The reference's own acceptance of the layer (tests/layers/flash_attn/test_sparse_attention.py:123-142):
+    cdf_threshold = 1.0 and sparsity = 0.0 keep every block, so the result is dense attention."""
+    from mindiesd import attention_forward, sparse_attention
+    q, k, v = (inputs.randn(70 + i, 1, 9600, 3, 128, dtype=torch.float16).cuda() for i in range(3))
+    out = sparse_attention(q, k, v, scale=128 ** -0.5, head_num=3, input_layout="BSND", inner_precise=0,
+                           sparse_type="ada_bsa", cdf_threshold=1.0, sparsity=0.0)
+    dense = attention_forward(q, k, v, head_first=False)
+    assert torch.equal(out, dense)
+    smask, sct = torch.ops.mindiesd.sparse_block_estimate(
+        query=q, key=k, input_layout="BSND", num_heads=3, num_key_value_heads=3, scale_value=128 ** -0.5 / 8,
+        threshold=1.0, causal=False, row_sparse=1.0)
+    assert bool((smask[..., :75] == 1).all()) and bool((sct == 75).all())
