@@ -9,7 +9,7 @@ GPU) runs the same layer sequence-parallel with the Ulysses wrapper, so the tota
 line.  Inputs are seeded synthetic tensors of the named shapes (no dataset exists for this path);
 3.1 GB of operands per step exceed the 126 MB L2, so no L2 flush is needed between steps.
 
-Other single-GPU workloads of the same path (`--workload sparse|sparse_layer|fp8|fp8_layer|mask|quant|rearrange|estimate|ada_layer|c2`) print the
+Other single-GPU workloads of the same path (`--workload sparse|sparse_layer|fp8|fp8_layer|mask|quant|rotate_quant|rearrange|estimate|ada_layer|c2`) print the
 same kind of line for their kernel; `--impl reference` times the CPU oracle (the reference's
 unfused torch formula) on the host cores for the same metric.
 """
@@ -286,7 +286,7 @@ def single_gpu_workload(args, device):
     cfg = workloads.C3
     peaks = measured_peaks()
     name = args.workload
-    src = workloads.C4 if name in ("fp8", "fp8_layer", "quant") else (workloads.C2 if name == "c2" else cfg)
+    src = workloads.C4 if name in ("fp8", "fp8_layer", "quant", "rotate_quant") else (workloads.C2 if name == "c2" else cfg)
     if args.heads:
         cfg = workloads.Config(cfg.name, cfg.batch, args.heads, cfg.grid, cfg.seq, cfg.dtype)
     q, k, v = workloads.make_qkv(src, device, seed=0, heads=args.heads or None)
@@ -373,6 +373,12 @@ def single_gpu_workload(args, device):
         del smask
         label = ("ada_bsa layer via mindiesd.sparse_attention(ada_bsa): block estimate + block-sparse attention, "
                  "B1 N40 S75600 D128")
+    elif name == "rotate_quant":
+        rot = torch.linalg.qr(torch.randn(128, 128, device=device, dtype=torch.float64))[0].to(q.dtype)
+        step = lambda: _cabi.fa_rotate_quant(q, rot, 128)  # noqa: E731
+        work = q.numel() * 3.0
+        unit, bound = "GB/s", "hbm"
+        label = "learned 128x128 rotation fused with e4m3 block quantisation of one operand, B1 N40 S75600 D128"
     elif name == "rearrange":
         step = lambda: _cabi.rf_rearrange(q, cfg.grid, 0, True)  # noqa: E731
         work = q.numel() * 4.0

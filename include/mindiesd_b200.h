@@ -251,6 +251,27 @@ typedef struct mindiesd_quant_args {
 int mindiesd_fa_block_quant(const mindiesd_quant_args* args, void* stream);
 
 /*
+ * Rotation by a learned matrix fused with the block quantisation:  y = x rot  per token
+ * (rot: [128, 128] row-major, the type of x), then mode-0 quantisation of y as above, the scale taken
+ * on the fp32 products.  y is never written: 2 bytes in, 1 byte out per element.
+ *
+ * Stands in for `query @ self.q_rot` / `key @ self.k_rot` followed by fa_block_quant_preprocess
+ * (mindiesd/quantization/layer.py:284-302).
+ */
+typedef struct mindiesd_rotate_quant_args {
+    const void* x;   /* [B, N, S, 128] bf16/fp16 by element strides */
+    const void* rot; /* [128, 128] contiguous */
+    void* out;       /* e4m3 [B, N, S, 128] contiguous, 16-byte aligned */
+    float* scales;   /* fp32 [B, N, ceil(S/row_block)] */
+    int32_t batch, heads, seq, head_dim; /* head_dim 128 */
+    int64_t x_stride[3];
+    int32_t dtype;
+    int32_t row_block; /* 128, 256 or 512 */
+} mindiesd_rotate_quant_args;
+
+int mindiesd_fa_rotate_quant(const mindiesd_rotate_quant_args* args, void* stream);
+
+/*
  * Sparse block estimate: the mask builder of adaptive block-sparse attention ("ada_bsa").
  *
  * Tokens are taken `stride` (8) at a time; the pooled logit of query group g and key group h is

@@ -30,6 +30,14 @@ inline int dtype_bytes(int dtype) {
 int encode_tile_map(CUtensorMap* map, const void* base, int dtype, int64_t channels, int64_t tokens,
                     int64_t heads, int64_t batch, const int64_t stride[3], int box_rows);
 
+// e4m3 block quantisation of x @ rot (rot: [128, 128] in x's type), the product kept in tensor memory.
+// The stored scale is absmax / 448 * post_scale.
+int rotate_quant_launch(const void* x, const int64_t x_stride[3], const void* rot, int dtype, int batch, int heads, int seq,
+                        int row_block, void* out, float* scales, float post_scale, cudaStream_t stream);
+// The same with the fixed 128-point Hadamard rotation (an exact +-1 matrix, 1/sqrt(128) in the scale).
+int hadamard_quant_launch(const void* x, const int64_t x_stride[3], int dtype, int batch, int heads, int seq, int row_block,
+                          void* out, float* scales, cudaStream_t stream);
+
 // Pooling + mask kernels of the RainFusion mask builder with the pooled means in `pooled`.
 int rf_block_mask_impl(const mindiesd_mask_args* a, float* pooled, size_t pooled_bytes, cudaStream_t stream);
 

@@ -19,32 +19,7 @@ struct QuantParams {
     int64_t stride[3];  // elements
     int heads, seq, row_block, blocks;
     int is_bf16;
-    int rotate;
 };
-
-// 128-point Walsh-Hadamard rotation (Sylvester order, scaled by 1/sqrt(128)) of one token row held
-// by 16 consecutive lanes x 8 channels.  Rotating q and k by the same orthogonal matrix leaves
-// q k^T unchanged while spreading outlier channels over all channels, which is what keeps the
-// e4m3 rounding error of the scores small.  Every lane of the warp must call this.
-__device__ __forceinline__ void hadamard128(float (&f)[8], int c) {
-#pragma unroll
-    for (int st = 1; st < 8; st <<= 1)
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-            if (!(i & st)) {
-                const float a = f[i], b = f[i | st];
-                f[i] = a + b;
-                f[i | st] = a - b;
-            }
-#pragma unroll
-    for (int m = 1; m < 16; m <<= 1) {
-        const float sign = (c & m) ? -1.0f : 1.0f;  // upper lane of a pair: other - mine
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = fmaf(f[i], sign, __shfl_xor_sync(0xffffffffu, f[i], m));
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] *= 0.08838834764831845f;
-}
 
 __device__ __forceinline__ void unpack8(const uint4& raw, int is_bf16, float (&f)[8]) {
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -73,11 +48,9 @@ __device__ __forceinline__ uint2 quant8(const float (&f)[8], float inv) {
                       static_cast<uint32_t>(h[2]) | (static_cast<uint32_t>(h[3]) << 16));
 }
 
-// mode 0.  Grid (row block, head, batch); 256 threads = 16 token rows x 16 vectors of 8 channels.
-// kTrips = row_block / 16 rows per thread.  kKeep: the rotated block stays in registers between the
-// absmax pass and the quantise pass, so the input is read and rotated once; otherwise the block is
-// read twice, the second time from L2.
-template <int kTrips, bool kKeep>
+// mode 0 without rotation.  Grid (row block, head, batch); 256 threads = 16 token rows x 16 vectors of 8
+// channels; kTrips = row_block / 16 rows per thread.  The block is read twice, the second time from L2.
+template <int kTrips>
 __global__ void __launch_bounds__(256) quant_block_kernel(const QuantParams p) {
     __shared__ float warp_max[8];
     const int blk = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
@@ -85,21 +58,16 @@ __global__ void __launch_bounds__(256) quant_block_kernel(const QuantParams p) {
     const int first = blk * p.row_block;
     const int count = min(p.row_block, p.seq - first);
     const uint16_t* base = static_cast<const uint16_t*>(p.x) + batch * p.stride[0] + head * p.stride[1];
-    float kept[kKeep ? kTrips : 1][8];
     float amax = 0.0f;
 #pragma unroll
-    for (int tr = 0; tr < kTrips; ++tr) {  // uniform trip count: the rotation shuffles across lanes
+    for (int tr = 0; tr < kTrips; ++tr) {
         const int r = tr * 16 + r0;
         uint4 raw = make_uint4(0, 0, 0, 0);
         if (r < count) raw = *reinterpret_cast<const uint4*>(base + (first + r) * p.stride[2] + c * 8);
         float f[8];
         unpack8(raw, p.is_bf16, f);
-        if (p.rotate) hadamard128(f, c);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            amax = fmaxf(amax, fabsf(f[i]));
-            if constexpr (kKeep) kept[tr][i] = f[i];
-        }
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
     }
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
@@ -116,17 +84,12 @@ __global__ void __launch_bounds__(256) quant_block_kernel(const QuantParams p) {
 #pragma unroll
     for (int tr = 0; tr < kTrips; ++tr) {
         const int r = tr * 16 + r0;
-        float f[8];
-        if constexpr (kKeep) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = kept[tr][i];
-        } else {
-            uint4 raw = make_uint4(0, 0, 0, 0);
-            if (r < count) raw = *reinterpret_cast<const uint4*>(base + (first + r) * p.stride[2] + c * 8);
+        if (r < count) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(base + (first + r) * p.stride[2] + c * 8);
+            float f[8];
             unpack8(raw, p.is_bf16, f);
-            if (p.rotate) hadamard128(f, c);
+            *reinterpret_cast<uint2*>(obase + static_cast<int64_t>(first + r) * 128 + c * 8) = quant8(f, inv);
         }
-        if (r < count) *reinterpret_cast<uint2*>(obase + static_cast<int64_t>(first + r) * 128 + c * 8) = quant8(f, inv);
     }
 }
 
@@ -212,20 +175,19 @@ extern "C" int mindiesd_fa_block_quant(const mindiesd_quant_args* a, void* strea
     p.heads = a->heads;
     p.seq = a->seq;
     p.is_bf16 = a->dtype == MINDIESD_BF16;
-    p.rotate = a->rotate ? 1 : 0;
     if (a->mode == 1 && a->rotate) return MINDIESD_E_VALUE;  // v is never rotated
     if (a->mode == 0) {
         if (a->row_block != 128 && a->row_block != 256 && a->row_block != 512) return MINDIESD_E_SHAPE;
         p.row_block = a->row_block;
         p.blocks = (a->seq + a->row_block - 1) / a->row_block;
         dim3 grid(p.blocks, a->heads, a->batch);
-        // Keeping the block in registers pays when the rotation would otherwise be done twice; without
-        // the rotation the lighter two-pass form (second read from L2) runs at copy speed.
-        if (a->rotate && a->row_block == 128) quant_block_kernel<8, true><<<grid, 256, 0, stream>>>(p);
-        else if (a->rotate && a->row_block == 256) quant_block_kernel<16, true><<<grid, 256, 0, stream>>>(p);
-        else if (a->row_block == 128) quant_block_kernel<8, false><<<grid, 256, 0, stream>>>(p);
-        else if (a->row_block == 256) quant_block_kernel<16, false><<<grid, 256, 0, stream>>>(p);
-        else quant_block_kernel<32, false><<<grid, 256, 0, stream>>>(p);
+        // The rotation is a 128x128 product: it runs on the tensor cores inside the quantiser.
+        if (a->rotate)
+            return hadamard_quant_launch(a->x, a->x_stride, a->dtype, a->batch, a->heads, a->seq, a->row_block, a->out,
+                                         a->scales, stream);
+        if (a->row_block == 128) quant_block_kernel<8><<<grid, 256, 0, stream>>>(p);
+        else if (a->row_block == 256) quant_block_kernel<16><<<grid, 256, 0, stream>>>(p);
+        else quant_block_kernel<32><<<grid, 256, 0, stream>>>(p);
     } else if (a->mode == 1) {
         p.row_block = 0;
         p.blocks = 0;

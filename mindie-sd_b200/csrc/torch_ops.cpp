@@ -575,6 +575,32 @@ std::tuple<at::Tensor, at::Tensor> fa_block_quant_cuda(const at::Tensor& x, int6
     return std::make_tuple(out, scales);
 }
 
+std::tuple<at::Tensor, at::Tensor> fa_rotate_quant_cuda(const at::Tensor& x, const at::Tensor& rot, int64_t block_size,
+                                                        bool head_first) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 4, "fa_rotate_quant: x must be a 4-D CUDA tensor");
+    TORCH_CHECK(rot.is_cuda() && rot.dim() == 2 && rot.size(0) == 128 && rot.size(1) == 128,
+                "fa_rotate_quant: rot must be a CUDA tensor [128, 128]");
+    at::Tensor src = x.stride(3) == 1 ? x : x.contiguous();
+    at::Tensor r = rot.to(src.scalar_type()).contiguous();
+    mindiesd_rotate_quant_args a = {};
+    a.x = src.data_ptr();
+    a.rot = r.data_ptr();
+    a.batch = static_cast<int32_t>(src.size(0));
+    a.heads = static_cast<int32_t>(src.size(head_first ? 1 : 2));
+    a.seq = static_cast<int32_t>(src.size(head_first ? 2 : 1));
+    a.head_dim = static_cast<int32_t>(src.size(3));
+    fill_strides(src, head_first, a.x_stride);
+    a.dtype = dtype_code(src.scalar_type());
+    a.row_block = static_cast<int32_t>(block_size);
+    at::Tensor out = at::empty({a.batch, a.heads, a.seq, a.head_dim}, src.options().dtype(at::kFloat8_e4m3fn));
+    at::Tensor scales = at::empty({a.batch, a.heads, (a.seq + block_size - 1) / block_size}, src.options().dtype(at::kFloat));
+    a.out = out.data_ptr();
+    a.scales = scales.data_ptr<float>();
+    c10::cuda::CUDAGuard guard(x.device());
+    check_rc(mindiesd_fa_rotate_quant(&a, stream_of(x)), "mindiesd_fa_rotate_quant");
+    return std::make_tuple(out, scales);
+}
+
 at::Tensor fp8_attention_cuda(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
                               const at::Tensor& q_scale, const at::Tensor& k_scale, const at::Tensor& v_scale,
                               double scale, int64_t k_block, int64_t v_block, at::ScalarType out_dtype) {
@@ -639,6 +665,7 @@ TORCH_LIBRARY(mindiesd, m) {
         "rf_mask_from_pooled(Tensor q_pooled, Tensor k_pooled, int[] latent_shape, int txt_len, float sparsity, "
         "int block_size, bool protect_first_frame, int temporal_band, bool return_lists) -> (Tensor, Tensor, Tensor)");
     m.def("fa_block_quant(Tensor x, int block_size, bool head_first, bool per_channel, bool rotate) -> (Tensor, Tensor)");
+    m.def("fa_rotate_quant(Tensor x, Tensor rot, int block_size, bool head_first) -> (Tensor, Tensor)");
     m.def(
         "fp8_attention(Tensor query, Tensor key, Tensor value, Tensor q_scale, Tensor k_scale, Tensor v_scale, "
         "float scale, int k_block, int v_block, ScalarType out_dtype) -> Tensor");
@@ -656,5 +683,6 @@ TORCH_LIBRARY_IMPL(mindiesd, CUDA, m) {
     m.impl("rf_pool", &rf_pool_cuda);
     m.impl("rf_mask_from_pooled", &rf_mask_from_pooled_cuda);
     m.impl("fa_block_quant", &fa_block_quant_cuda);
+    m.impl("fa_rotate_quant", &fa_rotate_quant_cuda);
     m.impl("fp8_attention", &fp8_attention_cuda);
 }

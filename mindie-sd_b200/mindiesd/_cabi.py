@@ -104,6 +104,15 @@ class QuantArgs(C.Structure):
     ]
 
 
+class RotateQuantArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("rot", C.c_void_p), ("out", C.c_void_p), ("scales", C.c_void_p),
+        ("batch", C.c_int32), ("heads", C.c_int32), ("seq", C.c_int32), ("head_dim", C.c_int32),
+        ("x_stride", C.c_int64 * 3),
+        ("dtype", C.c_int32), ("row_block", C.c_int32),
+    ]
+
+
 class EstimateArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("k", C.c_void_p),
@@ -141,7 +150,7 @@ def lib():
         handle.mindiesd_abi_version.restype = C.c_int
         for name in ("mindiesd_attention_fwd", "mindiesd_rf_rearrange", "mindiesd_rf_block_mask",
                      "mindiesd_rf_pool", "mindiesd_rf_mask_from_pooled", "mindiesd_fa_block_quant",
-                     "mindiesd_sparse_block_estimate"):
+                     "mindiesd_sparse_block_estimate", "mindiesd_fa_rotate_quant"):
             fn = getattr(handle, name, None)
             if fn is not None:
                 fn.restype = C.c_int
@@ -369,3 +378,19 @@ def sparse_block_estimate(q, k, scale, threshold, row_sparse=1.0, head_first=Tru
     check(lib().mindiesd_sparse_block_estimate(C.byref(a), current_stream_ptr(q.device)),
           "mindiesd_sparse_block_estimate")
     return mask, count
+
+
+def fa_rotate_quant(x, rot, row_block=128, head_first=True):
+    """mindiesd_fa_rotate_quant: (x @ rot) quantised to e4m3 in row_block-token blocks without
+    materialising the product.  Returns (e4m3 [B, N, S, D], fp32 scales [B, N, blocks])."""
+    b, n, s, d = _dims(x, head_first)
+    rot = rot.to(device=x.device, dtype=x.dtype).contiguous()
+    out = torch.empty(b, n, s, d, dtype=torch.float8_e4m3fn, device=x.device)
+    scales = torch.empty(b, n, (s + row_block - 1) // row_block, dtype=torch.float32, device=x.device)
+    a = RotateQuantArgs()
+    a.x, a.rot, a.out, a.scales = x.data_ptr(), rot.data_ptr(), out.data_ptr(), scales.data_ptr()
+    a.batch, a.heads, a.seq, a.head_dim = b, n, s, d
+    a.x_stride[:] = strides_bns(x, head_first)
+    a.dtype, a.row_block = dtype_code(x.dtype), row_block
+    check(lib().mindiesd_fa_rotate_quant(C.byref(a), current_stream_ptr(x.device)), "mindiesd_fa_rotate_quant")
+    return out, scales

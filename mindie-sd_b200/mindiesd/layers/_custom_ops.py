@@ -183,6 +183,14 @@ def _fa_block_quant_fake(x, block_size, head_first, per_channel, rotate):
     return x.new_empty([b, n, s, d], dtype=torch.float8_e4m3fn), x.new_empty([b, n, nscale], dtype=torch.float32)
 
 
+@register_ops.register_mindie_fake_op("fa_rotate_quant")
+def _fa_rotate_quant_fake(x, rot, block_size, head_first):
+    b, n, s, d = (x.shape[0], x.shape[1], x.shape[2], x.shape[3]) if head_first else \
+        (x.shape[0], x.shape[2], x.shape[1], x.shape[3])
+    return (x.new_empty([b, n, s, d], dtype=torch.float8_e4m3fn),
+            x.new_empty([b, n, (s + block_size - 1) // block_size], dtype=torch.float32))
+
+
 @register_ops.register_mindie_fake_op("fp8_attention")
 def _fp8_attention_fake(query, key, value, q_scale, k_scale, v_scale, scale, k_block, v_block, out_dtype):
     return query.new_empty(query.shape, dtype=out_dtype)

@@ -9,7 +9,9 @@ def fa_block_quant_preprocess(input_tensor, block_size=128, dst_type=torch.float
     """Returns (e4m3 [B, N, S, D], fp32 scales [B, N, ceil(S/block_size), 1]); real = stored * scale.
     `layout` ('BNSD' default, or 'BSND') names the input layout; the output is always BNSD.
     `rotate=True` first rotates every token by the 128-point Hadamard matrix / sqrt(128) inside the
-    same kernel (use it on q and k together: q k^T is unchanged, outlier channels are spread)."""
+    same kernel (use it on q and k together: q k^T is unchanged, outlier channels are spread).
+    `rot=` a [128, 128] matrix: the tokens are multiplied by it on the tensor cores inside the
+    quantisation kernel (the product is never written out)."""
     if len(input_tensor.shape) != 4:
         raise ParametersInvalid(f"fa block quant preprocess only support qkv quant, dim = 4, "
                                 f"but got {len(input_tensor.shape)}.")
@@ -20,8 +22,14 @@ def fa_block_quant_preprocess(input_tensor, block_size=128, dst_type=torch.float
     layout = kwargs.get("layout", "BNSD")
     if layout not in ("BNSD", "BSND"):
         raise ParametersInvalid(f"Unsupported layout: {layout}, expected 'BNSD' or 'BSND'.")
-    quant, scale = torch.ops.mindiesd.fa_block_quant(input_tensor, int(block_size), layout == "BNSD", False,
-                                                     bool(kwargs.get("rotate", False)))
+    rot = kwargs.get("rot")
+    if rot is not None:
+        if kwargs.get("rotate", False):
+            raise ParametersInvalid("give either rotate=True (fixed Hadamard rotation) or rot= (a matrix), not both.")
+        quant, scale = torch.ops.mindiesd.fa_rotate_quant(input_tensor, rot, int(block_size), layout == "BNSD")
+    else:
+        quant, scale = torch.ops.mindiesd.fa_block_quant(input_tensor, int(block_size), layout == "BNSD", False,
+                                                         bool(kwargs.get("rotate", False)))
     return quant, scale.unsqueeze(-1)
 
 

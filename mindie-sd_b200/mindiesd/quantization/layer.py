@@ -16,7 +16,8 @@ def get_quant_weight(weights, name):
 
 
 class FP8RotateQuantFA(nn.Module):
-    """forward(query, key, value, layout=): rotate q and k by the learned 128x128 matrices, quantise
+    """forward(query, key, value, layout=): rotate q and k by the learned 128x128 matrices (fused into
+    the quantisation kernel), quantise
     q (128-token blocks), k and v (256-token blocks) to e4m3, run FP8 attention, return the input
     dtype and layout.  Without learned matrices q and k are rotated by the fixed Hadamard matrix
     inside the quantisation kernel.  `v_per_channel=True` quantises v with one scale per channel."""
@@ -31,14 +32,12 @@ class FP8RotateQuantFA(nn.Module):
         layout = kwargs.get("layout", "BNSD")
         if layout not in ("BNSD", "BSND"):
             raise ValueError(f"Unsupported layout: {layout}, expected 'BNSD' or 'BSND'.")
-        if self.q_rot is not None:
-            query = torch.matmul(query, self.q_rot.to(query.dtype))
-        if self.k_rot is not None:
-            key = torch.matmul(key, self.k_rot.to(key.dtype))
         d = query.shape[-1]
         fixed = self.q_rot is None and self.k_rot is None
-        q, q_scale = fa_block_quant_preprocess(query, block_size=128, layout=layout, rotate=fixed)
-        k, k_scale = fa_block_quant_preprocess(key, block_size=256, layout=layout, rotate=fixed)
+        # A learned rotation runs on the tensor cores inside the quantisation kernel; without learned
+        # matrices both operands get the fixed Hadamard rotation, also inside that kernel.
+        q, q_scale = fa_block_quant_preprocess(query, block_size=128, layout=layout, rotate=fixed, rot=self.q_rot)
+        k, k_scale = fa_block_quant_preprocess(key, block_size=256, layout=layout, rotate=fixed, rot=self.k_rot)
         if self.v_per_channel:
             v, v_scale = fa_channel_quant_preprocess(value, layout=layout)
             v_block = 0

@@ -50,6 +50,50 @@ def test_rotated_block_quant_close_to_oracle():
     assert abs(a.norm().item() / x.float().norm().item() - 1) < 0.01
 
 
+@pytest.mark.parametrize("row_block,dtype,head_first", [(128, torch.bfloat16, True), (256, torch.float16, False),
+                                                        (512, torch.bfloat16, True)])
+def test_learned_rotation_fused_with_quant(row_block, dtype, head_first):
+    """x @ rot on the tensor cores inside the quantiser against the oracle's quantisation of the exact
+    product.  The kernel accumulates the products in fp32 in its own order, so scales agree to 1e-5
+    and the e4m3 bytes may differ where a value sits on a rounding boundary: compared on dequantised
+    values, within one e4m3 step."""
+    from mindiesd import _cabi
+    s = 1000
+    x = inputs.randn(96, 2, 3, s, 128, dtype=dtype)
+    x[..., 9] *= 8
+    rot = torch.linalg.qr(inputs.randn(97, 128, 128).double())[0].to(dtype)  # a random orthogonal matrix
+    y = (x.double() @ rot.double()).float()
+    want_q, want_s = oq.block_quant(y, row_block)
+    xin = x if head_first else x.transpose(1, 2).contiguous()
+    got_q, got_s = _cabi.fa_rotate_quant(xin.cuda(), rot.cuda(), row_block, head_first=head_first)
+    assert _cabi.device_status() == 0
+    assert got_q.shape == (2, 3, s, 128) and got_s.shape == want_s.shape
+    assert torch.allclose(got_s.cpu(), want_s, rtol=1e-5)
+    deq = lambda q8, sc: q8.float() * sc.repeat_interleave(row_block, 2)[:, :, :s, None]  # noqa: E731
+    a, b = deq(got_q.cpu(), got_s.cpu()), deq(want_q, want_s)
+    assert ((a - b).abs() <= 0.13 * b.abs() + 1e-3).all()
+    same = (got_q.cpu().view(torch.uint8) == want_q.view(torch.uint8)).float().mean().item()
+    assert same > 0.99, same
+    # through the operator and the layer function
+    import mindiesd  # noqa: F401
+    from mindiesd.layers.quant.block_quant import fa_block_quant_preprocess
+    q2, s2 = fa_block_quant_preprocess(xin.cuda(), block_size=row_block, layout="BNSD" if head_first else "BSND",
+                                       rot=rot.cuda())
+    assert torch.equal(q2.view(torch.uint8), got_q.view(torch.uint8)) and torch.equal(s2.squeeze(-1), got_s)
+
+
+def test_fp8_hook_with_learned_rotations():
+    """FP8RotateQuantFA with q_rot / k_rot weights (the reference's configuration) keeps the cosine bar."""
+    from mindiesd import FP8RotateQuantFA
+    q, k, v = _outlier_inputs(120, 2, 1500)
+    rot = torch.linalg.qr(inputs.randn(123, 128, 128).double())[0].to(torch.bfloat16)
+    hook = FP8RotateQuantFA("blk", {"blk.q_rot": rot, "blk.k_rot": rot}, v_per_channel=True).cuda()
+    out = hook(q.cuda(), k.cuda(), v.cuda(), layout="BNSD")
+    want = oa.attention_math(q.float(), k.float(), v.float(), head_first=True)
+    assert out.dtype == torch.bfloat16 and out.shape == q.shape
+    assert oq.cosine(out.cpu(), want) >= 0.995
+
+
 def _outlier_inputs(seed, n, s):
     q, k, v = (inputs.randn(seed + i, 1, n, s, 128, dtype=torch.bfloat16) for i in range(3))
     for x in (q, k, v):
