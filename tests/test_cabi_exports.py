@@ -38,7 +38,7 @@ def test_struct_layouts_match_the_header(tmp_path):
     structs = {"mindiesd_attn_args": _cabi.AttnArgs, "mindiesd_rearrange_args": _cabi.RearrangeArgs,
                "mindiesd_mask_args": _cabi.MaskArgs, "mindiesd_pool_args": _cabi.PoolArgs,
                "mindiesd_pooled_mask_args": _cabi.PooledMaskArgs, "mindiesd_quant_args": _cabi.QuantArgs,
-               "mindiesd_estimate_args": _cabi.EstimateArgs}
+               "mindiesd_estimate_args": _cabi.EstimateArgs, "mindiesd_rotate_quant_args": _cabi.RotateQuantArgs}
     src = tmp_path / "sz.c"
     body = "".join(f'printf("{n} %zu\\n", sizeof({n}));' for n in structs)
     src.write_text(f'#include <stdio.h>\n#include "mindiesd_b200.h"\nint main(void){{{body}return 0;}}\n')
@@ -64,6 +64,12 @@ def test_invalid_arguments_return_codes_without_a_gpu():
     assert lib.mindiesd_rf_rearrange(ctypes.byref(r), None) == -1
     q = _cabi.QuantArgs()
     assert lib.mindiesd_fa_block_quant(ctypes.byref(q), None) == -1
+    rq = _cabi.RotateQuantArgs()
+    assert lib.mindiesd_fa_rotate_quant(ctypes.byref(rq), None) == -1
+    rq.x = rq.rot = rq.out = rq.scales = 4096
+    rq.batch = rq.heads = 1
+    rq.seq, rq.head_dim, rq.row_block = 256, 128, 100
+    assert lib.mindiesd_fa_rotate_quant(ctypes.byref(rq), None) == -2  # row_block
     e = _cabi.EstimateArgs()
     assert lib.mindiesd_sparse_block_estimate(ctypes.byref(e), None) == -1
     e.q = e.k = e.mask = e.count = e.scratch = 4096
