@@ -8,6 +8,7 @@ activations).  The device side is two fixed sets of staging buffers ordered by e
 """
 from __future__ import annotations
 
+import threading
 from typing import Optional
 
 import torch
@@ -15,7 +16,9 @@ import torch
 from ...utils.exception import ParametersInvalid
 
 
-_STAGING = {}  # device index -> (key, buffers): one set of staging buffers per device, reused across calls
+_STAGING = {}  # device index -> (key, buffers, streams): one set of staging buffers per device, reused across calls
+_LOCKS = {}    # device index -> lock: calls on one device take turns (they share the staging buffers)
+_LOCKS_GUARD = threading.Lock()
 
 
 def _staging(device, shape, dtype):
@@ -64,6 +67,15 @@ def attention_forward_host(query: torch.Tensor, key: torch.Tensor, value: torch.
     if out is None:
         out = torch.empty(query.shape, dtype=query.dtype, pin_memory=True)
     hc = n // head_chunks
+    with _LOCKS_GUARD:
+        lock = _LOCKS.setdefault(device.index, threading.Lock())
+    with lock:
+        return _run_pipeline(query, key, value, out, scale, head_chunks, hc, device)
+
+
+def _run_pipeline(query, key, value, out, scale, head_chunks, hc, device):
+    from ... import _cabi
+    b, _, s, d = query.shape
     bufs, (copy_in, copy_out) = _staging(device, (b, hc, s, d), query.dtype)
     compute = torch.cuda.current_stream(device)
     copy_in.wait_stream(compute)
