@@ -207,7 +207,7 @@ def dense_or_ulysses(args, rank, world, device):
         step = lambda: _cabi.attention(q, k, v, head_first=False, out=out)  # noqa: E731
     else:
         from mindiesd.parallel import default_head_chunks
-        chunks = default_head_chunks(cfg.heads // world)
+        chunks = args.ulysses_chunks or default_head_chunks(cfg.heads // world, cfg.seq)
         launches_per_step = chunks
         step = lambda: ulysses_attention(q, k, v, head_chunks=chunks)  # noqa: E731
 
@@ -415,6 +415,7 @@ def main():
     ap.add_argument("--workload", default="dense")
     ap.add_argument("--sparsity", type=float, default=0.75)
     ap.add_argument("--band", type=int, default=-1)
+    ap.add_argument("--ulysses-chunks", type=int, default=0, help="head chunks per rank of the Ulysses leg (0: the API's default)")
     ap.add_argument("--e2e-chunks", type=int, default=0, help="head chunks of the pipelined end-to-end leg (0: the API's default)")
     ap.add_argument("--cdf", type=float, default=0.9, help="cumulative-mass threshold of the ada_bsa estimate")
     ap.add_argument("--heads", type=int, default=0, help="reduced head count for profiler captures (default: the full 40)")

@@ -81,3 +81,13 @@ def test_ulysses_rejects_indivisible_heads():
             ulysses_attention(q, q[:, :4], q)
     finally:
         dist.destroy_process_group()
+
+
+def test_default_head_chunks_keeps_pieces_large():
+    from mindiesd.parallel import default_head_chunks
+    # 75 600 tokens: 296 thread blocks per head, so a piece needs four heads for eight waves
+    assert default_head_chunks(5, 75600) == 1     # 8 GPUs
+    assert default_head_chunks(10, 75600) == 2    # 4 GPUs
+    assert default_head_chunks(20, 75600) == 5    # 2 GPUs
+    assert default_head_chunks(20, 4096) == 1     # short sequences: never below eight waves
+    assert default_head_chunks(12) == 6 and default_head_chunks(7) == 7  # length unknown: the largest divisor up to 8
