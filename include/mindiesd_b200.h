@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define MINDIESD_B200_ABI_VERSION 1
+#define MINDIESD_B200_ABI_VERSION 2
 
 enum {
     MINDIESD_OK = 0,
@@ -92,6 +92,36 @@ typedef struct mindiesd_attn_args {
     const float* v_scale;
     int32_t k_scale_block;
     int32_t v_scale_block;
+
+    /* Element strides of batch, head and token of lse; all zero = contiguous [B, N, seq_q]. */
+    int64_t lse_stride[3];
+
+    /* causal != 0: query i attends to key j only if j <= i + (seq_kv - seq_q), i.e. the triangle is
+       aligned to the last query and the last key (for seq_q == seq_kv the usual lower triangle).
+       This is sparse_mode 3 of npu_fusion_attention as mindiesd/layers/flash_attn/
+       attention_forward_varlen.py:133-149 calls it, and the in-block triangle of
+       ada_block_sparse_attention_cpu, tests/plugin/test_adablocksparseattention.py:69-72.  It combines
+       with a block mask or list (a block is walked if both allow it).  Rows that see no key give zeros. */
+    int32_t causal;
+
+    /* num_seqs > 0: q is [1, N, Tq, D] and k, v are [1, Nkv, Tk, D] holding num_seqs sequences packed
+       along the token axis (the TND layout of attention_forward_varlen, batch must be 1, seq_q = Tq,
+       seq_kv = Tk); cu_seqlens_q / cu_seqlens_kv are int32 device arrays [num_seqs + 1] of cumulative
+       token counts starting at 0.  Sequence i attends only to its own keys; with causal the triangle is
+       aligned per sequence.  One launch covers all sequences and the host never reads the arrays.
+       Not combined with a block mask / list or with e4m3 operands (MINDIESD_E_VALUE). */
+    int32_t num_seqs;
+    const int32_t* cu_seqlens_q;
+    const int32_t* cu_seqlens_kv;
+
+    /* Time limit of every bounded wait inside the kernel, microseconds; 0 = the default (1 s).  A wait
+       that runs out makes its thread block unwind, fill its output rows with NaN and set the device
+       status word (mindiesd_device_status). */
+    uint32_t wait_limit_us;
+    /* Test hook, 0 in production: non-zero makes the loader of every thread block withhold its first
+       key block (the copy is neither started nor announced), so that the consumer's wait runs into
+       wait_limit_us.  It exists to exercise the give-up path without faulting or hanging the GPU. */
+    int32_t test_withhold;
 } mindiesd_attn_args;
 
 int mindiesd_attention_fwd(const mindiesd_attn_args* args, void* stream);
@@ -321,6 +351,77 @@ typedef struct mindiesd_estimate_args {
 
 size_t mindiesd_sparse_block_estimate_scratch_bytes(int32_t batch, int32_t heads, int32_t seq);
 int mindiesd_sparse_block_estimate(const mindiesd_estimate_args* args, void* stream);
+
+/*
+ * Rotary position embedding:  out = x * cos + rotated(x) * sin  per token, with
+ * mode 1 ("rotated_half"):        rotated(x) = (-x[d/2:], x[:d/2])
+ * mode 2 ("rotated_interleaved"): rotated(x) = (-x1, x0, -x3, x2, ...).
+ * x/out: [B, N, S, D] by element strides (unit channel stride), bf16, fp16 or fp32, D even.
+ * cos/sin: contiguous [S, D] tables, fp32 or the type of x.  The arithmetic runs in the tables' type
+ * (fp32: both products and the sum rounded to fp32, one rounding to the type of x at the end), which is
+ * the reference's unfused formula bit for bit.  out may alias x when mode == 2 only.
+ *
+ * Stands in for torch_npu.npu_rotary_mul as called by rotary_position_embedding
+ * (mindiesd/layers/rope.py:54-115).
+ */
+typedef struct mindiesd_rope_args {
+    const void* x;
+    void* out;
+    const void* cos;
+    const void* sin;
+    int32_t batch, heads, seq, head_dim;
+    int64_t x_stride[3];   /* element strides of batch, head, token */
+    int64_t out_stride[3];
+    int32_t dtype;         /* MINDIESD_BF16 / FP16 / FP32 */
+    int32_t table_dtype;   /* MINDIESD_FP32 or dtype */
+    int32_t mode;          /* 1 half, 2 interleaved */
+} mindiesd_rope_args;
+
+int mindiesd_rope(const mindiesd_rope_args* args, void* stream);
+
+/*
+ * The re-shard step of Ulysses sequence parallelism as one data-movement kernel.
+ *
+ * A rank holds `rows` tokens with all N heads: tensors [rows, N, 128] addressed by a row and a head
+ * stride.  Rank r of `world` owns the heads [r * group_heads, (r + 1) * group_heads); a call moves
+ * the piece [head0, head0 + heads) of every rank's group.
+ *
+ * inverse == 0 (before attention): for every destination rank r the piece of tensor[0..n_src-1] (q, k, v)
+ *   is written to table[r] as [rows, n_src * heads, 128] (row stride table_row_stride, tensor i at head
+ *   slot i * heads).  table[r] may be chunk r of a local send buffer, or an address inside rank r's
+ *   receive buffer mapped into this process (peer memory): then the kernel IS the all-to-all, its
+ *   stores crossing NVLink.  With rope_mode != 0, tensor[0] and tensor[1] are rotated on the way by the
+ *   rotary embedding (fp32 tables [rows, 128] for this rank's tokens, arithmetic as mindiesd_rope).
+ * inverse == 1 (after attention): table[r] holds rank r's [rows, heads, 128] output block for this
+ *   rank's tokens; it is written to tensor[0][row, r * group_heads + head0 + j].
+ *
+ * bf16 / fp16, head_dim 128, every pointer and stride a multiple of 16 bytes.
+ * thread_blocks: how many to launch (0 = enough to fill the GPU); a small number leaves the SMs to an
+ * attention kernel running beside it.
+ *
+ * Stands in for the reshapes and the two torch.distributed all_to_all calls of the Ulysses pattern in
+ * docs/zh/features/parallelism.md:207-233, and, with rope_mode, for rotary_position_embedding
+ * (mindiesd/layers/rope.py:54-115) on q and k before them.
+ */
+#define MINDIESD_MAX_RANKS 8
+
+typedef struct mindiesd_ulysses_move_args {
+    const void* tensor[3];
+    void* table[MINDIESD_MAX_RANKS];
+    int64_t tensor_row_stride;  /* elements */
+    int64_t tensor_head_stride;
+    int64_t table_row_stride;
+    int32_t n_src;              /* 1..3 (inverse: 1) */
+    int32_t rows, world, group_heads, head0, heads, head_dim;
+    int32_t dtype;
+    int32_t inverse;
+    const float* cos;
+    const float* sin;
+    int32_t rope_mode;          /* 0 none, 1 half, 2 interleaved */
+    int32_t thread_blocks;
+} mindiesd_ulysses_move_args;
+
+int mindiesd_ulysses_move(const mindiesd_ulysses_move_args* args, void* stream);
 
 /*
  * Device status word of the current device: 0, or the code of the first bounded wait inside a

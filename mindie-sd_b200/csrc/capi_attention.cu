@@ -163,6 +163,29 @@ extern "C" int mindiesd_attention_fwd(const mindiesd_attn_args* a, void* stream)
         p.v_scale_block = a->v_scale_block;
         p.v_scale_count = a->v_scale_block ? (a->seq_kv + a->v_scale_block - 1) / a->v_scale_block : 128;
     }
+    if (a->lse_stride[0] || a->lse_stride[1] || a->lse_stride[2]) {
+        for (int i = 0; i < 3; ++i) {
+            if (a->lse_stride[i] < 0) return MINDIESD_E_STRIDE;
+            p.lse_stride[i] = a->lse_stride[i];
+        }
+    } else {
+        p.lse_stride[0] = static_cast<int64_t>(a->heads) * a->seq_q;
+        p.lse_stride[1] = a->seq_q;
+        p.lse_stride[2] = 1;
+    }
+    p.causal = a->causal != 0;
+    if (a->num_seqs < 0) return MINDIESD_E_VALUE;
+    if (a->num_seqs > 0) {
+        if (!a->cu_seqlens_q || !a->cu_seqlens_kv) return MINDIESD_E_NULL;
+        if (a->batch != 1) return MINDIESD_E_SHAPE;
+        if (fp8 || a->sparse_mode != MINDIESD_SPARSE_NONE) return MINDIESD_E_VALUE;
+        if (a->seq_q / 256 + static_cast<int64_t>(a->num_seqs) > 0x7fffffff) return MINDIESD_E_CAPACITY;
+        p.cu_seqlens_q = a->cu_seqlens_q;
+        p.cu_seqlens_kv = a->cu_seqlens_kv;
+        p.num_seqs = a->num_seqs;
+    }
+    p.wait_limit_us = a->wait_limit_us ? a->wait_limit_us : kDefaultWaitLimitUs;
+    p.test_withhold = a->test_withhold;
     p.status = device_status_word();
     const cudaError_t e = fa_fwd_launch(p, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? MINDIESD_OK : static_cast<int>(e);

@@ -32,6 +32,16 @@ constexpr int kMmaWarp = 8;
 constexpr int kLoadWarp = 9;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+// Register budgets after the roles split: 2 x 128 x kRegsSoftmax + 128 x kRegsOther <= 65536.
+#ifndef SDB_FA_REGS_SOFTMAX
+#define SDB_FA_REGS_SOFTMAX 224
+#endif
+#ifndef SDB_FA_REGS_OTHER
+#define SDB_FA_REGS_OTHER 64
+#endif
+constexpr int kRegsSoftmax = SDB_FA_REGS_SOFTMAX;
+constexpr int kRegsOther = SDB_FA_REGS_OTHER;
+static_assert(2 * 128 * kRegsSoftmax + 128 * kRegsOther <= 65536, "register file of one SM");
 constexpr float kRescaleThreshold = 8.0f;  // log2 units the running max may lag before O is rescaled
 constexpr float kFp8PShiftLog2 = 8.0f;     // e4m3 probabilities are stored as p * 2^8
 constexpr float kFp8Lag = 0.75f;           // 2^8.75 = 431 still fits e4m3 (max 448)
@@ -79,6 +89,23 @@ __device__ __forceinline__ uint32_t pack_quad_e4m3(float a, float b, float c, fl
     return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
 }
 
+// Fills one output row (and its log-sum-exp) with NaN: what a thread block leaves behind when it did not
+// compute its rows, so that a result produced after a wait gave up can never pass for a real one.
+__device__ __forceinline__ void poison_row(const FaParams& p, int batch, int head, int q_row) {
+    const int64_t off = batch * p.o_stride[0] + head * p.o_stride[1] + static_cast<int64_t>(q_row) * p.o_stride[2];
+    if (p.out_dtype == 2) {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<float*>(p.out) + off);
+        const uint4 nan4 = make_uint4(0x7fc00000u, 0x7fc00000u, 0x7fc00000u, 0x7fc00000u);
+        for (int i = 0; i < kHeadDim / 4; ++i) dst[i] = nan4;
+    } else {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + off);
+        const uint32_t n2 = p.out_dtype == 0 ? 0x7fc07fc0u : 0x7e007e00u;
+        const uint4 nan4 = make_uint4(n2, n2, n2, n2);
+        for (int i = 0; i < kHeadDim / 8; ++i) dst[i] = nan4;
+    }
+    if (p.lse) p.lse[batch * p.lse_stride[0] + head * p.lse_stride[1] + q_row * p.lse_stride[2]] = __int_as_float(0x7fc00000);
+}
+
 }  // namespace
 
 // kIn: element type of q/k/v and of the stored probabilities (0 bf16, 1 fp16, 3 e4m3).
@@ -104,7 +131,8 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     // the P V product runs while the second half of the exponentials is still being taken.  Two-byte
     // operands hand a block over whole, on the second barrier.
     auto bar_p = [&](int t, int h) { return bar_base + 8u * (3 + 2 * C::kStages + 2 * t + h); };
-    constexpr int kNumBars = 7 + 2 * C::kStages;
+    auto bar_done = [&]() { return bar_base + 8u * (7 + 2 * C::kStages); };
+    constexpr int kNumBars = 8 + 2 * C::kStages;
     static_assert(kNumBars * 8 + 16 <= 256, "barrier area");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -113,17 +141,52 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const int qpair = blockIdx.x;
     const int head = blockIdx.y;
     const int batch = blockIdx.z;
     const int kv_head = head / (p.heads / p.kv_heads);
+    // The sequence this thread block works on: the whole token axis, or -- packed variable-length
+    // sequences -- the one its tile pair falls into.  Rows and keys below are counted from the start of
+    // that sequence; q_base / k_base are where it starts on the token axis.
+    int qpair = blockIdx.x;
+    int q_base = 0, k_base = 0, q_len = p.seq_q, k_len = p.seq_kv;
+    if (p.cu_seqlens_q) {
+        int i = 0;
+        for (; i < p.num_seqs; ++i) {
+            const int pairs = (p.cu_seqlens_q[i + 1] - p.cu_seqlens_q[i] + 2 * kTile - 1) / (2 * kTile);
+            if (qpair < pairs) break;
+            qpair -= pairs;
+        }
+        if (i == p.num_seqs) return;  // the grid is an upper bound on the number of tile pairs
+        q_base = p.cu_seqlens_q[i];
+        q_len = p.cu_seqlens_q[i + 1] - q_base;
+        k_base = p.cu_seqlens_kv[i];
+        k_len = p.cu_seqlens_kv[i + 1] - k_base;
+    } else if (p.causal) {
+        qpair = static_cast<int>(gridDim.x) - 1 - qpair;  // the tiles with the most visible keys start first
+    }
     const int q_row0 = qpair * 2 * kTile;
-    const bool tile1_valid = q_row0 + kTile < p.seq_q;
-    const int nkb = p.kv_blocks;
+    const bool tile1_valid = q_row0 + kTile < q_len;
+    const int nkb = p.cu_seqlens_q ? min((k_len + kTile - 1) / kTile, kMaxKvBlocks) : p.kv_blocks;
+    // Causal attention, aligned to the last query and the last key of the sequence: query i sees key j
+    // iff j <= i + causal_off.  vis[t]: key blocks tile t can see at all.
+    const int causal_off = k_len - q_len;
+    int vis[2] = {nkb, nkb};
+    if (p.causal) {
+        for (int t = 0; t < 2; ++t) {
+            const int last_key = q_row0 + t * kTile + kTile - 1 + causal_off;  // of the tile's last row
+            vis[t] = last_key < 0 ? 0 : min(nkb, last_key / kTile + 1);
+        }
+    }
 
     // A grid in which one CTA already gave up a wait is not going to produce a usable result: the
     // remaining CTAs leave at once instead of each running into its own time-out.
-    if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
+    // The decision is taken once per thread block: all of its threads stay or all leave (the ones that stay
+    // set up barriers and tensor memory for the others).  A block that leaves marks its rows.
+    if (__syncthreads_or(tid == 0 && p.status && *reinterpret_cast<volatile int*>(p.status) != 0)) {
+        if (tid < 2 * kTile && q_row0 + tid < q_len) poison_row(p, batch, head, q_base + q_row0 + tid);
+        return;
+    }
+    const uint32_t wait_us = p.wait_limit_us;
 
     // ---- set-up -------------------------------------------------------------------------------
     if (tid == 0) {
@@ -137,6 +200,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             mbar_init(bar_p(t, 0), kTile);
             mbar_init(bar_p(t, 1), kTile);
         }
+        mbar_init(bar_done(), 1);
         *abort_flag = 0;
         *abort_site = 0;
         fence_mbar_init();
@@ -158,16 +222,16 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         const int qb0 = qpair * 2;
         if (p.sparse_mode == 0) {
             for (int j = tid; j < nkb; j += kThreads) {
-                f0[j] = 1;
-                f1[j] = tile1_valid ? 1 : 0;
+                f0[j] = j < vis[0];
+                f1[j] = tile1_valid && j < vis[1];
             }
         } else if (p.sparse_mode == 1) {
             const int8_t* m0 = p.block_mask + batch * p.mask_stride[0] + head * p.mask_stride[1] +
                                static_cast<int64_t>(qb0) * p.mask_stride[2];
             const int8_t* m1 = m0 + p.mask_stride[2];
             for (int j = tid; j < nkb; j += kThreads) {
-                f0[j] = m0[j] != 0;
-                f1[j] = tile1_valid ? (m1[j] != 0) : 0;
+                f0[j] = m0[j] != 0 && j < vis[0];
+                f1[j] = tile1_valid && m1[j] != 0 && j < vis[1];
             }
         } else {
             for (int j = tid; j < nkb; j += kThreads) {
@@ -183,7 +247,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 uint8_t* f = t ? f1 : f0;
                 for (int i = tid; i < n; i += kThreads) {
                     const int64_t id = ids[i];
-                    if (id >= 0 && id < nkb) f[id] = 1;
+                    if (id >= 0 && id < vis[t]) f[id] = 1;
                 }
             }
         }
@@ -200,7 +264,13 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         return j < nkb ? j : -1;
     };
 
-    if (warp == kLoadWarp) {
+    // The softmax warps hold a whole score row and the packed probabilities of a block in registers
+    // (about 200 live values); the loader, the MMA thread and the two idle warps need a few dozen.
+    // The launch gives every thread 168: the last warpgroup hands most of its registers back and
+    // each softmax warpgroup takes its share.
+    if (warp >= 8) {
+      warpgroup_reg_dec<kRegsOther>();
+      if (warp == kLoadWarp) {
         // ---- TMA producer ---------------------------------------------------------------------
         if (lane == 0) {
             const uint32_t q_bytes = (tile1_valid ? 2 : 1) * C::kTileBytes;
@@ -208,29 +278,37 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             for (int t = 0; t < (tile1_valid ? 2 : 1); ++t)
                 for (int a = 0; a < C::kAtoms; ++a)
                     tma_load_4d(smem_u32(sm_q + t * C::kTileBytes + a * C::kAtomBytes), &p.tm_q, bar_q(),
-                                a * C::kBoxInner, q_row0 + t * kTile, head, batch);
+                                a * C::kBoxInner, q_base + q_row0 + t * kTile, head, batch);
             Ring ring;
-            int issued = 0;
+            int issued = 0, withheld = -1;
             bool ok = true;
             for (int u = next_block(0); u >= 0 && ok; u = next_block(u + 1)) {
                 for (int which = 0; which < 2 && ok; ++which) {  // 0: K block, 1: V block
-                    ok = mbar_wait(bar_empty(ring.idx), ring.phase ^ 1u, abort_flag, 1);
+                    ok = mbar_wait(bar_empty(ring.idx), ring.phase ^ 1u, abort_flag, 1, wait_us);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(bar_full(ring.idx), C::kTileBytes);
-                    const CUtensorMap* tm = which ? &p.tm_v : &p.tm_k;
-                    for (int a = 0; a < C::kAtoms; ++a)
-                        tma_load_4d(smem_u32(sm_ring + ring.idx * C::kTileBytes + a * C::kAtomBytes), tm,
-                                    bar_full(ring.idx), a * C::kBoxInner, u * kTile, kv_head, batch);
+                    if (p.test_withhold && issued == 0) {
+                        // Host-side failure injection for the tests of the bounded waits: the first copy is
+                        // neither started nor announced, so its barrier never completes, the consumer's wait
+                        // runs into the limit and the thread block unwinds.  Nothing is in flight for it.
+                        withheld = 0;
+                    } else {
+                        mbar_arrive_expect_tx(bar_full(ring.idx), C::kTileBytes);
+                        const CUtensorMap* tm = which ? &p.tm_v : &p.tm_k;
+                        for (int a = 0; a < C::kAtoms; ++a)
+                            tma_load_4d(smem_u32(sm_ring + ring.idx * C::kTileBytes + a * C::kAtomBytes), tm,
+                                        bar_full(ring.idx), a * C::kBoxInner, k_base + u * kTile, kv_head, batch);
+                    }
                     ring.template next<C::kStages>();
                     ++issued;
                 }
             }
             // Before the CTA may exit, every copy this thread started must have landed.
-            mbar_wait(bar_q(), 0, abort_flag, 2);
+            mbar_wait_drain(bar_q(), 0);
             const int pending = issued < C::kStages ? issued : C::kStages;
             for (int i = 0; i < pending; ++i) {
                 const int n = issued - 1 - i;  // n-th load overall
-                mbar_wait(bar_full(n % C::kStages), static_cast<uint32_t>(n / C::kStages) & 1u, abort_flag, 3);
+                if (n == withheld) continue;   // never started
+                mbar_wait_drain(bar_full(n % C::kStages), static_cast<uint32_t>(n / C::kStages) & 1u);
             }
         }
     } else if (warp == kMmaWarp) {
@@ -266,12 +344,12 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 }
             };
 
-            bool ok = mbar_wait(bar_q(), 0, abort_flag, 10);
+            bool ok = mbar_wait(bar_q(), 0, abort_flag, 10, wait_us);
             Ring ring;
             int pv_cnt[2] = {0, 0};
             int u = next_block(0);
             if (ok && u >= 0) {
-                ok = mbar_wait(bar_full(ring.idx), ring.phase, abort_flag, 11);
+                ok = mbar_wait(bar_full(ring.idx), ring.phase, abort_flag, 11, wait_us);
                 if (ok) {
                     tc_fence_after();
                     const int f = flags_of(u);
@@ -290,16 +368,16 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 const Ring kslot = ring;
                 if (nf) ring.template next<C::kStages>();
 
-                ok = mbar_wait(bar_full(vslot.idx), vslot.phase, abort_flag, 12);
+                ok = mbar_wait(bar_full(vslot.idx), vslot.phase, abort_flag, 12, wait_us);
                 if (!ok) break;
                 if (f & 1) {
                     if constexpr (kFp8) {
-                        ok = mbar_wait(bar_p(0, 0), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13);
+                        ok = mbar_wait(bar_p(0, 0), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13, wait_us);
                         if (!ok) break;
                         tc_fence_after();
                         issue_pv(0, 0, vslot.idx, pv_cnt[0] > 0);
                     }
-                    ok = mbar_wait(bar_p(0, 1), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13);
+                    ok = mbar_wait(bar_p(0, 1), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13, wait_us);
                     if (!ok) break;
                     tc_fence_after();
                     if constexpr (!kFp8) issue_pv(0, 0, vslot.idx, pv_cnt[0] > 0);
@@ -307,19 +385,19 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     ++pv_cnt[0];
                 }
                 if (nf) {
-                    ok = mbar_wait(bar_full(kslot.idx), kslot.phase, abort_flag, 17);
+                    ok = mbar_wait(bar_full(kslot.idx), kslot.phase, abort_flag, 17, wait_us);
                     if (!ok) break;
                     tc_fence_after();
                 }
                 if (nf & 1) issue_s(0, kslot.idx);
                 if (f & 2) {
                     if constexpr (kFp8) {
-                        ok = mbar_wait(bar_p(1, 0), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14);
+                        ok = mbar_wait(bar_p(1, 0), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14, wait_us);
                         if (!ok) break;
                         tc_fence_after();
                         issue_pv(1, 0, vslot.idx, pv_cnt[1] > 0);
                     }
-                    ok = mbar_wait(bar_p(1, 1), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14);
+                    ok = mbar_wait(bar_p(1, 1), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14, wait_us);
                     if (!ok) break;
                     tc_fence_after();
                     if constexpr (!kFp8) issue_pv(1, 0, vslot.idx, pv_cnt[1] > 0);
@@ -334,8 +412,15 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             // Final arrival on each tile's S barrier: its output accumulator is complete.
             umma_commit(bar_s(0));
             umma_commit(bar_s(1));
+            if (!ok) {
+                // Unwinding: tensor memory is about to be freed, so the products already issued must be over.
+                umma_commit(bar_done());
+                mbar_wait_drain(bar_done(), 0);
+            }
         }
-    } else if (warp < 8) {
+      }
+    } else {
+        warpgroup_reg_inc<kRegsSoftmax>();
         // ---- softmax, O rescale, epilogue: one query row per thread ------------------------------
         const int t = warp >> 2;  // tile of this warpgroup
         const int row_in_tile = tid & (kTile - 1);
@@ -344,7 +429,8 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         const uint32_t taddr_s = tmem_base + (t ? kColS1 : kColS0) + lane_base;
         const uint32_t taddr_o = tmem_base + (t ? kColO1 : kColO0) + lane_base;
         const uint8_t* my_flags = t ? f1 : f0;
-        const int tail_valid = p.seq_kv - (nkb - 1) * kTile;  // valid columns of the last kv block
+        const int tail_valid = k_len - (nkb - 1) * kTile;  // valid columns of the last kv block
+        const int tile_last_key = q_row0 + t * kTile + causal_off;  // last key the tile's FIRST row sees
         // The running max may lag the true max by this much (log2 units) before O is rescaled; the
         // probabilities then reach 2^lag, which two-byte formats hold but e4m3 does not.
         constexpr float kLag = kFp8 ? kFp8Lag : kRescaleThreshold;
@@ -376,7 +462,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         bool ok = true;
         for (int j = 0; j < nkb; ++j) {
             if (!my_flags[j]) continue;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_s(t), static_cast<uint32_t>(cnt) & 1u, abort_flag, 20 + t));
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_s(t), static_cast<uint32_t>(cnt) & 1u, abort_flag, 20 + t, wait_us));
             if (!ok) break;
             tc_fence_after();
 
@@ -395,14 +481,22 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     l_fix = 1.0f / r;
                 }
             }
-            const bool tail = j == nkb - 1 && tail_valid < kTile;
-            if (tail) {
+            // Columns this row may not see in this block: beyond the end of the keys (last block) or, with
+            // causal attention, beyond the row's own position (the blocks the tile's diagonal crosses).
+            bool masked = j == nkb - 1 && tail_valid < kTile;  // warp-uniform
+            int n_seen = masked ? tail_valid : kTile;
+            if (p.causal && j * kTile + kTile - 1 > tile_last_key) {
+                masked = true;
+                n_seen = min(n_seen, q_row + causal_off - j * kTile + 1);
+            }
+            auto mask_scores = [&]() {
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (c * 32 + i >= tail_valid) s[c][i] = 0xff800000u;  // -inf
-            }
+                        if (c * 32 + i >= n_seen) s[c][i] = 0xff800000u;  // -inf
+            };
+            if (masked) mask_scores();
             auto row_max = [&]() {
                 // Eight independent chains of three-input max: a single running max would be 128 dependent
                 // instructions.
@@ -433,7 +527,9 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 // first blocks -- are the scores fetched again (nothing has been stored over them yet), the
                 // block's own max taken, O and the running sum rescaled, and the probabilities redone.  The
                 // first block has no running max yet and takes its own first.
-                if (cnt == 0) m_run = row_max() * mult;
+                // A row that sees no key of its first block sees none at all (causal): any finite max
+                // gives it zero probabilities and a zero sum.
+                if (cnt == 0) m_run = fmaxf(row_max() * mult, -3.0e38f);
                 const uint64_t mult2 = pack2(mult, mult);
                 uint32_t pk[4][16];
                 float sum = 0.0f;
@@ -469,13 +565,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     #pragma unroll
                     for (int c = 0; c < 4; ++c) tmem_ld32(taddr_s + c * 32, s[c]);
                     tmem_wait_ld();
-                    if (tail) {
-    #pragma unroll
-                        for (int c = 0; c < 4; ++c)
-    #pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                if (c * 32 + i >= tail_valid) s[c][i] = 0xff800000u;  // -inf
-                    }
+                    if (masked) mask_scores();
                     const float m_new = fmaxf(m_run, row_max() * mult);
                     const float alpha = ex2_approx(m_run - m_new);
                     m_run = m_new;
@@ -508,7 +598,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 float alpha = 1.0f;
                 if (rescale) {
                     const float m_new = fmaxf(m_run, m_cand);
-                    alpha = ex2_approx(m_run - m_new);  // 0 on the first block (m_run = -inf)
+                    alpha = m_new == -INFINITY ? 0.0f : ex2_approx(m_run - m_new);  // 0 on the first block (m_run = -inf)
                     l_run *= alpha;
                     m_run = m_new;
                     // The (rare, after the first blocks) rescale of O must be over before the first half
@@ -527,7 +617,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     }
                 }
                 // x = s * mult - m as packed pairs (one instruction per two scores), then ex2 and pack.
-                const float neg_m = kFp8 ? (kFp8PShiftLog2 + v_off - m_run) : -m_run;
+                const float neg_m = m_run == -INFINITY ? 0.0f : (kFp8 ? (kFp8PShiftLog2 + v_off - m_run) : -m_run);
                 const uint64_t mult2 = pack2(mult, mult), negm2 = pack2(neg_m, neg_m);
                 uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
     #pragma unroll
@@ -567,17 +657,17 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             }
             ++cnt;
         }
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_s(t), static_cast<uint32_t>(cnt) & 1u, abort_flag, 26 + t));
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_s(t), static_cast<uint32_t>(cnt) & 1u, abort_flag, 26 + t, wait_us));
         if (ok && (t == 0 || tile1_valid)) {  // warp-uniform: the tensor-memory loads are warp-collective
             tc_fence_after();
-            const bool row_ok = q_row < p.seq_q;
+            const bool row_ok = q_row < q_len;
             // l_run carries the 2^8 shift of the stored e4m3 probabilities, so it cancels in O / l.
             const float inv_l = l_run > 0.0f ? v_ref / l_run : 0.0f;
             const float* v_ch = (kFp8 && p.v_scale_block == 0)
                                     ? p.v_scale + (static_cast<int64_t>(batch) * p.kv_heads + kv_head) * kHeadDim
                                     : nullptr;
             uint8_t* orow = static_cast<uint8_t*>(p.out) +
-                            (batch * p.o_stride[0] + head * p.o_stride[1] + static_cast<int64_t>(q_row) * p.o_stride[2]) *
+                            (batch * p.o_stride[0] + head * p.o_stride[1] + static_cast<int64_t>(q_base + q_row) * p.o_stride[2]) *
                                 (p.out_dtype == 2 ? 4 : 2);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -619,7 +709,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             }
             if (p.lse && row_ok) {
                 const float shift = kFp8 ? kFp8PShiftLog2 : 0.0f;
-                p.lse[(static_cast<int64_t>(batch) * p.heads + head) * p.seq_q + q_row] =
+                p.lse[batch * p.lse_stride[0] + head * p.lse_stride[1] + (q_base + q_row) * p.lse_stride[2]] =
                     l_run > 0.0f ? (m_run - shift) * 0.6931471805599453f + logf(l_run) : -INFINITY;
             }
         }
@@ -632,6 +722,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
+    if (*abort_flag && tid < 2 * kTile && q_row0 + tid < q_len) poison_row(p, batch, head, q_base + q_row0 + tid);
     if (tid == 0 && *abort_flag && p.status) {
         // First CTA to report wins the word and leaves where it stopped behind it.
         if (atomicCAS(p.status, 0, kStatusFaWaitGaveUp) == 0) {
@@ -650,7 +741,9 @@ static cudaError_t launch_one(const FaParams& p, cudaStream_t stream) {
     const int smem = fa_fwd_smem_bytes(kIn == 3);
     cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<kIn>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    dim3 grid((p.seq_q + 2 * kTile - 1) / (2 * kTile), p.heads, p.batch);
+    // Packed sequences: every sequence rounds its tile pairs up, so seq_q / 256 + num_seqs bounds their number.
+    const int pairs = p.cu_seqlens_q ? p.seq_q / (2 * kTile) + p.num_seqs : (p.seq_q + 2 * kTile - 1) / (2 * kTile);
+    dim3 grid(pairs, p.heads, p.batch);
     fa_fwd_kernel<kIn><<<grid, kThreads, smem, stream>>>(p);
     return cudaGetLastError();
 }

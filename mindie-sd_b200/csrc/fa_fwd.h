@@ -11,6 +11,9 @@ constexpr int kMaxKvBlocks = 4096;  // key/value blocks of 128 tokens one launch
 // Status codes written to the device status word by kernels whose bounded waits gave up.
 constexpr int kStatusFaWaitGaveUp = 101;
 
+// Default time limit, in microseconds, of the bounded waits inside the kernels.
+constexpr uint32_t kDefaultWaitLimitUs = 1000000u;
+
 struct FaParams {
     // Rank-4 tiled tensor maps over (channel, token, head, batch); box = 128 bytes x 128 tokens.
     alignas(64) CUtensorMap tm_q;
@@ -18,12 +21,20 @@ struct FaParams {
     alignas(64) CUtensorMap tm_v;
     void* out;
     float* lse;
+    int64_t lse_stride[3];  // element strides of batch, head, token
     int64_t o_stride[3];  // element strides of batch, head, token
     int batch, heads, kv_heads, seq_q, seq_kv;
     int q_blocks, kv_blocks;
     int in_dtype;   // 0 bf16, 1 fp16, 3 e4m3
     int out_dtype;  // 0 bf16, 1 fp16, 2 fp32
     float scale_log2;  // softmax scale * log2(e)
+
+    int causal;  // query i sees key j iff j <= i + (seq_kv - seq_q), per sequence
+    // Packed variable-length sequences (batch 1): cumulative token counts [num_seqs + 1] on the device;
+    // seq_q / seq_kv are then the totals.  NULL: one sequence per batch entry.
+    const int32_t* cu_seqlens_q;
+    const int32_t* cu_seqlens_kv;
+    int num_seqs;
 
     int sparse_mode;  // 0 dense, 1 int8 mask, 2 compacted list
     const int8_t* block_mask;
@@ -39,6 +50,8 @@ struct FaParams {
     int v_scale_block, v_scale_count;
 
     int* status;
+    uint32_t wait_limit_us;  // time limit of every bounded wait of this launch
+    int test_withhold;       // failure injection for tests: the loader withholds its first copy
 };
 
 int fa_fwd_smem_bytes(bool fp8);

@@ -85,7 +85,10 @@ __global__ void __launch_bounds__(kThreads) rotq_kernel(const __grid_constant__ 
     const int blk = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
     const int row0 = blk * kTiles * kTile;
 
-    if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
+    // A grid in which one thread block already gave up a wait leaves at once.  The decision is taken
+    // once per thread block (all of its threads stay or all leave: the ones that stay set up barriers
+    // and tensor memory for the others).
+    if (__syncthreads_or(tid == 0 && p.status && *reinterpret_cast<volatile int*>(p.status) != 0)) return;
 
     if (tid == 0) {
         for (int i = 0; i < kNumBars; ++i) mbar_init(bar_base + 8u * i, 1);
@@ -120,9 +123,10 @@ __global__ void __launch_bounds__(kThreads) rotq_kernel(const __grid_constant__ 
             const uint32_t idesc = umma_idesc(kFmt, kTile, kTile, false, true);
             const uint32_t r_lo = desc_lo(smem_u32(sm_r), kAtomBytes);  // MN-major: 16 KB between the 64-column atoms
             bool ok = mbar_wait(bar_r(), 0, abort_flag, 1);
+            if (!ok) mbar_wait_drain(bar_r(), 0);
             for (int i = 0; i < kTiles; ++i) {
                 // Every started copy is waited for, also after a wait has given up.
-                const bool landed = mbar_wait(bar_x(i), 0, abort_flag, 2);
+                const bool landed = ok ? mbar_wait(bar_x(i), 0, abort_flag, 2) : mbar_wait_drain(bar_x(i), 0);
                 ok = ok && landed;
                 if (!ok) continue;
                 tc_fence_after();

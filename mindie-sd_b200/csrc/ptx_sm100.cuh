@@ -1,6 +1,6 @@
 // Thin inline-PTX wrappers for the sm_100a features the attention kernels use:
 // mbarriers, TMA tiled loads, tensor memory (TMEM) management, tcgen05 MMA / load / store.
-// Every wait is bounded: a wait that gives up returns false and the caller unwinds.
+// Every wait is bounded in time: a wait that gives up returns false and the caller unwinds.
 #pragma once
 #include <cuda_runtime.h>
 #include <cuda.h>
@@ -39,23 +39,61 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Spin limit of a bounded wait.  try_wait itself suspends the thread for a hardware-chosen
-// interval (of the order of a microsecond), so this many attempts is tens of milliseconds to a
-// second: far beyond any legitimate wait inside a kernel, short enough that a grid of stuck
-// CTAs still drains in seconds.
-constexpr uint32_t kSpinLimit = 1u << 18;
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
-// Waits for the phase with the given parity.  Returns false if the wait gave up (limit reached
-// or another role of the CTA raised the abort flag); the first to give up raises the flag and
-// leaves `site` (a small number naming the wait) next to it.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site = 0) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+// Time limit of a bounded wait.  The longest legitimate wait inside these kernels is that of the
+// warps of an idle query tile, which sit on one barrier for the whole life of their thread block:
+// tens of milliseconds at the largest sizes and the lowest clocks.  One second is far beyond that
+// and short enough that a grid of stuck thread blocks drains at once (the blocks that are resident
+// give up together; the ones that start afterwards see the status word and leave).
+constexpr uint32_t kWaitLimitUs = 1000000u;
+
+// Waits for the phase with the given parity, for at most limit_us microseconds of wall-clock time
+// (the nanosecond timer of the device, which does not depend on the SM clock).  Returns false if
+// the wait gave up (limit reached, or another role of the thread block raised the abort flag); the
+// first to give up raises the flag and leaves `site` (a small number naming the wait) next to it.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site = 0,
+                                          uint32_t limit_us = kWaitLimitUs) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && *abort_flag) return false;
+        if ((i & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > static_cast<uint64_t>(limit_us) * 1000u) break;
+        }
     }
     if (*abort_flag == 0) abort_flag[1] = site;
     *abort_flag = 1;
     return false;
+}
+
+// The wait of a thread that must see its own asynchronous copies land before the thread block may
+// exit: it does not look at the abort flag (the copies are in flight whatever the other roles
+// decided) and is bounded by time alone.
+__device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity, uint32_t limit_us = kWaitLimitUs) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t i = 1;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 0u && global_timer_ns() - t0 > static_cast<uint64_t>(limit_us) * 1000u) return false;
+    }
+}
+
+// Register budget of the calling warpgroup (four consecutive warps, all of which execute this):
+// a warpgroup that needs few registers hands them back so that another can take more than the
+// launch gave it.
+template <int kRegs>
+__device__ __forceinline__ void warpgroup_reg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void warpgroup_reg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
 }
 
 // ----------------------------------------------------------------------------------------------

@@ -101,7 +101,10 @@ __global__ void __launch_bounds__(kThreads1, 1) sbe_partial_kernel(const __grid_
     const int head = pair % p.heads, batch = pair / p.heads;
     const int kv_head = head / (p.heads / p.kv_heads);
 
-    if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
+    // A grid in which one thread block already gave up a wait leaves at once.  The decision is taken
+    // once per thread block (all of its threads stay or all leave: the ones that stay set up barriers
+    // and tensor memory for the others).
+    if (__syncthreads_or(tid == 0 && p.status && *reinterpret_cast<volatile int*>(p.status) != 0)) return;
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -152,7 +155,7 @@ __global__ void __launch_bounds__(kThreads1, 1) sbe_partial_kernel(const __grid_
             const int pending = issued < kStages ? issued : kStages;
             for (int i = 0; i < pending; ++i) {
                 const int n = issued - 1 - i;
-                mbar_wait(bar_full(n % kStages), static_cast<uint32_t>(n / kStages) & 1u, abort_flag, 2);
+                mbar_wait_drain(bar_full(n % kStages), static_cast<uint32_t>(n / kStages) & 1u);
             }
         }
     } else if (warp == kMmaWarp) {

@@ -9,6 +9,7 @@
 #include <torch/library.h>
 
 #include <stdexcept>
+#include <limits>
 #include <string>
 #include <tuple>
 #include <vector>
@@ -62,11 +63,20 @@ struct SparseSpec {
     const at::Tensor* select_num = nullptr;
 };
 
+// What only some operators pass on: the causal triangle, where the log-sum-exp goes, packed sequences.
+struct AttnExtra {
+    bool causal = false;
+    int64_t lse_stride[3] = {0, 0, 0};   // elements: batch, head, token; all zero = contiguous [B, N, S]
+    const at::Tensor* cu_seqlens_q = nullptr;  // int32 [num_seqs + 1] on the device (q, k, v then have batch 1)
+    const at::Tensor* cu_seqlens_kv = nullptr;
+};
+
 // q/k/v viewed as [B, *, *, D] in BNSD (head_first) or BSND order.  seq_q/seq_kv < 0: take from the view.
 void run_attention(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& out, float* lse,
                    bool head_first, double scale, const SparseSpec& sp, int64_t seq_q = -1, int64_t seq_kv = -1,
                    const at::Tensor* q_scale = nullptr, const at::Tensor* k_scale = nullptr,
-                   const at::Tensor* v_scale = nullptr, int k_block = 0, int v_block = 0) {
+                   const at::Tensor* v_scale = nullptr, int k_block = 0, int v_block = 0,
+                   const AttnExtra& extra = AttnExtra()) {
     TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda(), "mindiesd: q, k, v must be CUDA tensors");
     TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "mindiesd: q, k, v must be 4-D");
     TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type(),
@@ -117,6 +127,19 @@ void run_attention(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v
         a.v_scale = v_scale->data_ptr<float>();
         a.k_scale_block = k_block;
         a.v_scale_block = v_block;
+    }
+    a.causal = extra.causal ? 1 : 0;
+    for (int i = 0; i < 3; ++i) a.lse_stride[i] = extra.lse_stride[i];
+    if (extra.cu_seqlens_q) {
+        const at::Tensor& cq = *extra.cu_seqlens_q;
+        const at::Tensor& ck = *extra.cu_seqlens_kv;
+        TORCH_CHECK(cq.is_cuda() && ck.is_cuda() && cq.scalar_type() == at::kInt && ck.scalar_type() == at::kInt &&
+                        cq.dim() == 1 && ck.dim() == 1 && cq.is_contiguous() && ck.is_contiguous() &&
+                        cq.numel() == ck.numel() && cq.numel() >= 2,
+                    "mindiesd: cu_seqlens_q and cu_seqlens_k must be contiguous CUDA int32 vectors of one length >= 2");
+        a.num_seqs = static_cast<int32_t>(cq.numel() - 1);
+        a.cu_seqlens_q = cq.data_ptr<int32_t>();
+        a.cu_seqlens_kv = ck.data_ptr<int32_t>();
     }
     c10::cuda::CUDAGuard guard(q.device());
     check_rc(mindiesd_attention_fwd(&a, stream_of(q)), "mindiesd_attention_fwd");
@@ -187,10 +210,12 @@ std::tuple<at::Tensor, at::Tensor> block_sparse_attention_cuda(
         at::Tensor k4 = key.view({b, lens_kv[0], key.size(1), key.size(2)});
         at::Tensor v4 = value.view({b, lens_kv[0], value.size(1), value.size(2)});
         at::Tensor o4 = out.view({b, lens_q[0], query.size(1), query.size(2)});
-        at::Tensor lse_bns;
-        if (softmax_lse_flag != 0) lse_bns = at::empty({b, query.size(1), lens_q[0]}, lse.options());
-        run_attention(q4, k4, v4, o4, softmax_lse_flag != 0 ? lse_bns.data_ptr<float>() : nullptr, false, scale_value, sp);
-        if (softmax_lse_flag != 0) lse.copy_(lse_bns.permute({0, 2, 1}).reshape({query.size(0), query.size(1), 1}));
+        AttnExtra ex;  // lse [T, N, 1] = [B, S, N]: the kernel writes it through strides
+        ex.lse_stride[0] = lens_q[0] * query.size(1);
+        ex.lse_stride[1] = 1;
+        ex.lse_stride[2] = query.size(1);
+        run_attention(q4, k4, v4, o4, softmax_lse_flag != 0 ? lse.data_ptr<float>() : nullptr, false, scale_value, sp, -1,
+                      -1, nullptr, nullptr, nullptr, 0, 0, ex);
     } else {
         int64_t sq = -1, skv = -1;
         if (actual_seq_lengths.has_value()) {
@@ -205,9 +230,16 @@ std::tuple<at::Tensor, at::Tensor> block_sparse_attention_cuda(
             for (auto x : l) TORCH_CHECK(x == l[0] && x <= key.size(2), "block_sparse_attention: sequences must share one length");
             skv = l[0];
         }
-        if (sq >= 0 && sq < query.size(2)) out.zero_();
+        AttnExtra ex;  // lse is [B, N, S, 1] with S the padded length: rows past the real length stay -inf
+        ex.lse_stride[0] = query.size(1) * query.size(2);
+        ex.lse_stride[1] = query.size(2);
+        ex.lse_stride[2] = 1;
+        if (sq >= 0 && sq < query.size(2)) {
+            out.zero_();
+            if (softmax_lse_flag != 0) lse.fill_(-std::numeric_limits<float>::infinity());
+        }
         run_attention(query, key, value, out, softmax_lse_flag != 0 ? lse.data_ptr<float>() : nullptr, true, scale_value,
-                      sp, sq, skv);
+                      sp, sq, skv, nullptr, nullptr, nullptr, 0, 0, ex);
     }
     return std::make_tuple(out, lse);
 }
@@ -359,7 +391,6 @@ at::Tensor ada_block_sparse_attention_cuda(const at::Tensor& query, const at::Te
                                            int64_t inner_precise, int64_t pre_tokens, int64_t next_tokens,
                                            c10::OptionalIntArrayRef actual_seq_lengths,
                                            c10::OptionalIntArrayRef actual_seq_lengths_kv) {
-    TORCH_CHECK(!causal, "ada_block_sparse_attention: causal=True is not supported");
     TORCH_CHECK(sparse_size == 128, "ada_block_sparse_attention: only sparse_size=128 is supported");
     TORCH_CHECK(!actual_seq_lengths.has_value() && !actual_seq_lengths_kv.has_value(),
                 "ada_block_sparse_attention: actual_seq_lengths are not supported");
@@ -375,16 +406,39 @@ at::Tensor ada_block_sparse_attention_cuda(const at::Tensor& query, const at::Te
     SparseSpec sp;
     sp.mode = MINDIESD_SPARSE_MASK;
     sp.mask = &sparse_mask;
-    run_attention(q4, k4, v4, o4, nullptr, head_first, scale_value, sp);
+    AttnExtra ex;
+    ex.causal = causal;  // token-level triangle inside the blocks the mask keeps
+    run_attention(q4, k4, v4, o4, nullptr, head_first, scale_value, sp, -1, -1, nullptr, nullptr, nullptr, 0, 0, ex);
     return out;
 }
 
 // ---- dense attention in the caller's layout ---------------------------------------------------------
 at::Tensor attention_fwd_cuda(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, double scale,
-                              bool head_first) {
+                              bool head_first, bool causal) {
     at::Tensor out = at::empty_like(query);
     if (!out.is_contiguous() && out.stride(3) != 1) out = at::empty(query.sizes(), query.options());
-    run_attention(query, key, value, out, nullptr, head_first, scale, SparseSpec{});
+    AttnExtra ex;
+    ex.causal = causal;
+    run_attention(query, key, value, out, nullptr, head_first, scale, SparseSpec{}, -1, -1, nullptr, nullptr, nullptr, 0, 0,
+                  ex);
+    return out;
+}
+
+// ---- packed variable-length sequences (TND): one launch, sequence boundaries read on the device ------------
+at::Tensor attention_varlen_fwd_cuda(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
+                                     const at::Tensor& cu_seqlens_q, const at::Tensor& cu_seqlens_k, double scale,
+                                     bool causal) {
+    TORCH_CHECK(query.dim() == 3 && key.dim() == 3 && value.dim() == 3, "attention_varlen_fwd: q, k, v are (T, N, D)");
+    at::Tensor q = query.stride(2) == 1 ? query : query.contiguous();
+    at::Tensor k = key.stride(2) == 1 ? key : key.contiguous();
+    at::Tensor v = value.stride(2) == 1 ? value : value.contiguous();
+    at::Tensor out = at::empty(q.sizes(), q.options());
+    at::Tensor q4 = q.unsqueeze(0), k4 = k.unsqueeze(0), v4 = v.unsqueeze(0), o4 = out.unsqueeze(0);  // [1, T, N, D]
+    AttnExtra ex;
+    ex.causal = causal;
+    ex.cu_seqlens_q = &cu_seqlens_q;
+    ex.cu_seqlens_kv = &cu_seqlens_k;
+    run_attention(q4, k4, v4, o4, nullptr, false, scale, SparseSpec{}, -1, -1, nullptr, nullptr, nullptr, 0, 0, ex);
     return out;
 }
 
@@ -642,8 +696,6 @@ TORCH_LIBRARY(mindiesd, m) {
         "int num_key_value_heads=1, float scale_value=1.0, int inner_precise=0, "
         "int[]? actual_seq_lengths=None, int[]? actual_seq_lengths_kv=None, "
         "int softmax_lse_flag=0) -> (Tensor, Tensor)");
-    // Operators without a counterpart schema in the reference library: there the same steps are
-    // torch_npu calls or eager torch code.
     m.def(
         "ada_block_sparse_attention(Tensor query, Tensor key, Tensor value, Tensor sparse_mask, Tensor sparse_count_table, "
         "str input_layout='BNSD', int sparse_size=128, int num_heads=1, int num_key_value_heads=1, float scale_value=1, "
@@ -654,7 +706,12 @@ TORCH_LIBRARY(mindiesd, m) {
         "int[]? actual_seq_lengths_kv=None, str input_layout='BNSD', int stride=8, int sparse_size=128, "
         "int num_heads=1, int num_key_value_heads=1, float scale_value=1, float threshold=1, bool causal=True, "
         "bool keep_sink=True, bool keep_recent=True, float row_sparse=1) -> (Tensor, Tensor)");
-    m.def("attention_fwd(Tensor query, Tensor key, Tensor value, float scale, bool head_first) -> Tensor");
+    // Operators without a counterpart schema in the reference library: there the same steps are
+    // torch_npu calls or eager torch code.
+    m.def("attention_fwd(Tensor query, Tensor key, Tensor value, float scale, bool head_first, bool causal=False) -> Tensor");
+    m.def(
+        "attention_varlen_fwd(Tensor query, Tensor key, Tensor value, Tensor cu_seqlens_q, Tensor cu_seqlens_k, "
+        "float scale, bool causal=False) -> Tensor");
     m.def("rf_rearrange(Tensor x, int[] latent_shape, int txt_len, str input_layout, bool inverse) -> Tensor");
     m.def(
         "rf_block_mask(Tensor query, Tensor key, int[] latent_shape, int txt_len, float sparsity, float scale, "
@@ -678,6 +735,7 @@ TORCH_LIBRARY_IMPL(mindiesd, CUDA, m) {
     m.impl("ada_block_sparse_attention", &ada_block_sparse_attention_cuda);
     m.impl("sparse_block_estimate", &sparse_block_estimate_cuda);
     m.impl("attention_fwd", &attention_fwd_cuda);
+    m.impl("attention_varlen_fwd", &attention_varlen_fwd_cuda);
     m.impl("rf_rearrange", &rf_rearrange_cuda);
     m.impl("rf_block_mask", &rf_block_mask_cuda);
     m.impl("rf_pool", &rf_pool_cuda);

@@ -45,6 +45,10 @@ class AttnArgs(C.Structure):
         ("select_idx", C.c_void_p), ("select_num", C.c_void_p),
         ("q_scale", C.c_void_p), ("k_scale", C.c_void_p), ("v_scale", C.c_void_p),
         ("k_scale_block", C.c_int32), ("v_scale_block", C.c_int32),
+        ("lse_stride", C.c_int64 * 3),
+        ("causal", C.c_int32), ("num_seqs", C.c_int32),
+        ("cu_seqlens_q", C.c_void_p), ("cu_seqlens_kv", C.c_void_p),
+        ("wait_limit_us", C.c_uint32), ("test_withhold", C.c_int32),
     ]
 
 
@@ -127,6 +131,33 @@ class EstimateArgs(C.Structure):
     ]
 
 
+MAX_RANKS = 8
+
+
+class RopeArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("out", C.c_void_p), ("cos", C.c_void_p), ("sin", C.c_void_p),
+        ("batch", C.c_int32), ("heads", C.c_int32), ("seq", C.c_int32), ("head_dim", C.c_int32),
+        ("x_stride", C.c_int64 * 3), ("out_stride", C.c_int64 * 3),
+        ("dtype", C.c_int32), ("table_dtype", C.c_int32), ("mode", C.c_int32),
+    ]
+
+
+class UlyssesMoveArgs(C.Structure):
+    _fields_ = [
+        ("tensor", C.c_void_p * 3), ("table", C.c_void_p * MAX_RANKS),
+        ("tensor_row_stride", C.c_int64), ("tensor_head_stride", C.c_int64), ("table_row_stride", C.c_int64),
+        ("n_src", C.c_int32), ("rows", C.c_int32), ("world", C.c_int32), ("group_heads", C.c_int32),
+        ("head0", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+        ("dtype", C.c_int32), ("inverse", C.c_int32),
+        ("cos", C.c_void_p), ("sin", C.c_void_p),
+        ("rope_mode", C.c_int32), ("thread_blocks", C.c_int32),
+    ]
+
+
+ROPE_HALF, ROPE_INTERLEAVED = 1, 2
+
+
 def library_path() -> Path:
     override = os.environ.get("MINDIESD_B200_LIB")
     if override:
@@ -150,7 +181,8 @@ def lib():
         handle.mindiesd_abi_version.restype = C.c_int
         for name in ("mindiesd_attention_fwd", "mindiesd_rf_rearrange", "mindiesd_rf_block_mask",
                      "mindiesd_rf_pool", "mindiesd_rf_mask_from_pooled", "mindiesd_fa_block_quant",
-                     "mindiesd_sparse_block_estimate", "mindiesd_fa_rotate_quant"):
+                     "mindiesd_sparse_block_estimate", "mindiesd_fa_rotate_quant", "mindiesd_rope",
+                     "mindiesd_ulysses_move"):
             fn = getattr(handle, name, None)
             if fn is not None:
                 fn.restype = C.c_int
@@ -213,8 +245,11 @@ def _dims(x, head_first):
 
 def attention(q, k, v, head_first=True, scale=None, block_mask=None, select_idx=None, select_num=None,
               out_dtype=None, want_lse=False, q_scale=None, k_scale=None, v_scale=None, k_scale_block=0,
-              v_scale_block=0, out=None):
-    """mindiesd_attention_fwd on the current stream.  Returns out, or (out, lse) when want_lse."""
+              v_scale_block=0, out=None, causal=False, cu_seqlens_q=None, cu_seqlens_kv=None, wait_limit_us=0,
+              test_withhold=0):
+    """mindiesd_attention_fwd on the current stream.  Returns out, or (out, lse) when want_lse.
+    cu_seqlens_q / cu_seqlens_kv (int32 device tensors [num_seqs + 1]) select the packed
+    variable-length form: q, k, v are then [1, N, T, D] (head_first) or [1, T, N, D]."""
     b, n, sq, d = _dims(q, head_first)
     _, nkv, skv, _ = _dims(k, head_first)
     if out is None:
@@ -244,6 +279,14 @@ def attention(q, k, v, head_first=True, scale=None, block_mask=None, select_idx=
     if q_scale is not None:
         a.q_scale, a.k_scale, a.v_scale = q_scale.data_ptr(), k_scale.data_ptr(), v_scale.data_ptr()
         a.k_scale_block, a.v_scale_block = k_scale_block, v_scale_block
+    a.causal = int(bool(causal))
+    if cu_seqlens_q is not None:
+        for name, t in (("cu_seqlens_q", cu_seqlens_q), ("cu_seqlens_kv", cu_seqlens_kv)):
+            if t is None or t.dtype != torch.int32 or t.device != q.device or not t.is_contiguous():
+                raise NativeLibraryError(f"{name} must be a contiguous int32 tensor on the device of q")
+        a.num_seqs = cu_seqlens_q.numel() - 1
+        a.cu_seqlens_q, a.cu_seqlens_kv = cu_seqlens_q.data_ptr(), cu_seqlens_kv.data_ptr()
+    a.wait_limit_us, a.test_withhold = int(wait_limit_us), int(test_withhold)
     check(lib().mindiesd_attention_fwd(C.byref(a), current_stream_ptr(q.device)), "mindiesd_attention_fwd")
     return (out, lse) if want_lse else out
 
@@ -394,3 +437,40 @@ def fa_rotate_quant(x, rot, row_block=128, head_first=True):
     a.dtype, a.row_block = dtype_code(x.dtype), row_block
     check(lib().mindiesd_fa_rotate_quant(C.byref(a), current_stream_ptr(x.device)), "mindiesd_fa_rotate_quant")
     return out, scales
+
+
+def rope(x, cos, sin, mode, head_first=False, out=None):
+    """mindiesd_rope: x [B, N, S, D] (head_first) or [B, S, N, D]; cos/sin contiguous [S, D] tables in fp32
+    or the type of x; mode ROPE_HALF / ROPE_INTERLEAVED."""
+    b, n, s, d = _dims(x, head_first)
+    if out is None:
+        out = torch.empty_like(x)
+    a = RopeArgs()
+    a.x, a.out, a.cos, a.sin = x.data_ptr(), out.data_ptr(), cos.data_ptr(), sin.data_ptr()
+    a.batch, a.heads, a.seq, a.head_dim = b, n, s, d
+    a.x_stride[:] = strides_bns(x, head_first)
+    a.out_stride[:] = strides_bns(out, head_first)
+    a.dtype, a.table_dtype, a.mode = dtype_code(x.dtype), dtype_code(cos.dtype), int(mode)
+    check(lib().mindiesd_rope(C.byref(a), current_stream_ptr(x.device)), "mindiesd_rope")
+    return out
+
+
+def ulysses_move(tensors, table_ptrs, table_row_stride, rows, world, group_heads, head0, heads, inverse=False,
+                 cos=None, sin=None, rope_mode=0, thread_blocks=0):
+    """mindiesd_ulysses_move on the current stream.  tensors: this rank's [rows, N, 128] views (q, k, v; or
+    the output when inverse), all with the strides of the first; table_ptrs: one device address per rank."""
+    t0 = tensors[0]
+    a = UlyssesMoveArgs()
+    for i, t in enumerate(tensors):
+        if t.stride(-1) != 1 or t.stride() != t0.stride() or t.dtype != t0.dtype:
+            raise NativeLibraryError("ulysses_move: the tensors must share dtype and strides, channels contiguous")
+        a.tensor[i] = t.data_ptr()
+    for r, ptr in enumerate(table_ptrs):
+        a.table[r] = int(ptr)
+    a.tensor_row_stride, a.tensor_head_stride, a.table_row_stride = t0.stride(-3), t0.stride(-2), int(table_row_stride)
+    a.n_src, a.rows, a.world, a.group_heads, a.head0, a.heads = len(tensors), rows, world, group_heads, head0, heads
+    a.head_dim, a.dtype, a.inverse = t0.shape[-1], dtype_code(t0.dtype), int(inverse)
+    if rope_mode:
+        a.cos, a.sin, a.rope_mode = cos.data_ptr(), sin.data_ptr(), int(rope_mode)
+    a.thread_blocks = int(thread_blocks)
+    check(lib().mindiesd_ulysses_move(C.byref(a), current_stream_ptr(t0.device)), "mindiesd_ulysses_move")

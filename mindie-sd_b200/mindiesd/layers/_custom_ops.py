@@ -131,8 +131,13 @@ def _ada_block_sparse_attention_fake(query, key, value, sparse_mask, sparse_coun
 # ---- operators that replace torch_npu calls or eager torch code of the reference ---------------------
 
 @register_ops.register_mindie_fake_op("attention_fwd")
-def _attention_fwd_fake(query, key, value, scale, head_first):
+def _attention_fwd_fake(query, key, value, scale, head_first, causal=False):
     return torch.empty_like(query)
+
+
+@register_ops.register_mindie_fake_op("attention_varlen_fwd")
+def _attention_varlen_fwd_fake(query, key, value, cu_seqlens_q, cu_seqlens_k, scale, causal=False):
+    return query.new_empty(query.shape)
 
 
 @register_ops.register_mindie_fake_op("rf_rearrange")

@@ -2,9 +2,11 @@
 (mindiesd/layers/flash_attn/attention_forward_varlen.py:59-149 of MindIE-SD).
 
 Same signature and the same rejections as the reference (every reserved argument must stay None,
-dropout 0).  Each sequence is one launch of the dense kernel on a [1, len, N, D] view of the packed
-tensor, so nothing is copied or padded.  `causal=True` is rejected: video-DiT self-attention is not
-causal and the kernel has no causal mode.
+dropout 0).  All sequences go to the kernel in ONE launch, as the reference hands them to one fused
+call (:142-149): the kernel reads the cumulative lengths on the device and every thread block finds
+the sequence its query tiles belong to, so nothing is copied or padded and the host never reads a
+length.  `causal=True` is the reference's sparse_mode 3 (:133-138): the triangle is aligned to the
+last query and the last key of each sequence.
 """
 import math
 from dataclasses import dataclass
@@ -56,23 +58,23 @@ def attention_forward_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: 
         q=q, k=k, v=v, max_seqlen_q=max_seqlen_q, max_seqlen_k=max_seqlen_k, dropout_p=dropout_p,
         window_size=window_size, softcap=softcap, alibi_slopes=alibi_slopes, deterministic=deterministic,
         return_attn_probs=return_attn_probs, block_table=block_table))
-    if causal:
-        raise ParametersInvalid("causal=True is not supported by the B200 attention kernel.")
     head_dim = q.shape[-1]
     if softmax_scale is None:
         softmax_scale = head_dim ** -0.5
-    bounds_q = [int(x) for x in cu_seqlens_q]
-    bounds_k = [int(x) for x in cu_seqlens_k]
-    if len(bounds_q) != len(bounds_k) or len(bounds_q) < 2 or bounds_q[-1] != q.shape[0] or bounds_k[-1] != k.shape[0]:
+    cu_q = _as_device_int32(cu_seqlens_q, q.device)
+    cu_k = _as_device_int32(cu_seqlens_k, q.device)
+    if cu_q.dim() != 1 or cu_q.shape != cu_k.shape or cu_q.numel() < 2:
         raise ParametersInvalid("cu_seqlens_q / cu_seqlens_k must hold batch + 1 cumulative lengths ending at T.")
-    out = torch.empty_like(q)
-    for i in range(len(bounds_q) - 1):
-        q0, q1, k0, k1 = bounds_q[i], bounds_q[i + 1], bounds_k[i], bounds_k[i + 1]
-        if q1 <= q0:
-            continue
-        if k1 <= k0:
-            out[q0:q1].zero_()
-            continue
-        out[q0:q1] = torch.ops.mindiesd.attention_fwd(q[q0:q1].unsqueeze(0), k[k0:k1].unsqueeze(0),
-                                                      v[k0:k1].unsqueeze(0), float(softmax_scale), False)[0]
-    return out
+    if not isinstance(cu_seqlens_q, torch.Tensor) or not cu_seqlens_q.is_cuda:
+        # Host-side lengths can be checked without touching the device.
+        if int(cu_seqlens_q[-1]) != q.shape[0] or int(cu_seqlens_k[-1]) != k.shape[0]:
+            raise ParametersInvalid("cu_seqlens_q / cu_seqlens_k must hold batch + 1 cumulative lengths ending at T.")
+    return torch.ops.mindiesd.attention_varlen_fwd(q, k, v, cu_q, cu_k, float(softmax_scale), bool(causal))
+
+
+def _as_device_int32(cu_seqlens, device):
+    """The cumulative lengths as an int32 vector on `device`: a list, a list of 0-d tensors (the
+    reference's annotation), a host tensor or a device tensor.  A device tensor is used as it is."""
+    if isinstance(cu_seqlens, torch.Tensor):
+        return cu_seqlens.to(device=device, dtype=torch.int32).contiguous()
+    return torch.tensor([int(x) for x in cu_seqlens], dtype=torch.int32, device=device)

@@ -3,54 +3,129 @@ an all-to-all turns that into the full sequence with a slice of the heads, atten
 and a second all-to-all turns the result back.
 
 MindIE-SD documents this pattern (docs/zh/features/parallelism.md:207-233) without shipping it;
-this is the same tensor contract -- BSND in, BSND out, `N % world_size == 0` -- with two additions:
-q, k and v travel in ONE all-to-all per head chunk (stacked along the head axis), and the local
-heads are cut into chunks so that the exchange of chunk c+1 and the return of chunk c-1 run on a
-communication stream while chunk c's attention runs on the compute stream.
+this is the same tensor contract -- BSND in, BSND out, `N % world_size == 0` -- built differently:
+
+* The local heads are cut into pieces.  Per piece ONE kernel (`mindiesd_ulysses_move`) reads this
+  rank's q, k and v in place and writes, for every destination rank, the block that rank needs in
+  the layout its attention kernel reads -- optionally applying the rotary embedding to q and k on the
+  way -- and ONE all-to-all carries q, k and v together.  For B = 1 the receive buffer already is
+  `[S, 3h, D]`, which the attention kernel reads through strides; it writes its output straight into
+  the send buffer of the return exchange, and one kernel scatters the returned blocks into the result.
+* The exchange of piece c+1 and the return of piece c-1 run on a communication stream under piece
+  c's attention.  Pieces may be uneven (5 local heads -> 2 + 3), so that overlap exists at every
+  world size.
+* Send and receive buffers are allocated once per (shape, dtype, group) and reused by every call.
 """
 from __future__ import annotations
 
-from typing import Callable, Optional
+from typing import Callable, Optional, Sequence, Union
 
 import torch
 import torch.distributed as dist
 
 from ..utils.exception import ParametersInvalid
 
+_ROPE_MODES = {"rotated_half": 1, "rotated_interleaved": 2}
 
-def _default_attention(q, k, v, scale):
+
+def _default_attention(q, k, v, scale, out=None):
     # BSND views with a non-unit head-group stride: the kernel reads them through strides.
+    if out is not None and q.is_cuda:
+        from .. import _cabi
+        return _cabi.attention(q, k, v, head_first=False, scale=scale, out=out)
     return torch.ops.mindiesd.attention_fwd(q, k, v, float(scale), False)
 
 
-class _Streams:
-    """Compute/communication stream pair with event hand-over; on CPU every method is a no-op."""
+_COMM_STREAMS = {}
+_BUFFERS = {}
 
-    def __init__(self, device):
-        self.cuda = device.type == "cuda"
-        if self.cuda:
-            self.compute = torch.cuda.current_stream(device)
-            self.comm = _comm_stream(device)
 
-    def comm_after_compute(self):
-        if self.cuda:
-            ev = torch.cuda.Event()
-            ev.record(self.compute)
-            self.comm.wait_event(ev)
+def _comm_stream(device):
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _COMM_STREAMS:
+        _COMM_STREAMS[key] = torch.cuda.Stream(device=device, priority=-1)
+    return _COMM_STREAMS[key]
 
-    def compute_after_comm(self):
-        if self.cuda:
-            ev = torch.cuda.Event()
-            ev.record(self.comm)
-            return ev
-        return None
 
-    def wait(self, ev):
-        if self.cuda and ev is not None:
-            self.compute.wait_event(ev)
+def _buffers(key, shapes, dtype, device):
+    """Persistent send/receive buffers of one call signature.  Allocating them per call makes the
+    caching allocator grow and synchronise in the middle of the overlapped pipeline."""
+    cached = _BUFFERS.get(key)
+    if cached is None:
+        if len(_BUFFERS) >= 4:  # a handful of shapes per process; older ones go back to the allocator
+            _BUFFERS.pop(next(iter(_BUFFERS)))
+        cached = [torch.empty(s, dtype=dtype, device=device) for s in shapes]
+        _BUFFERS[key] = cached
+    return cached
 
-    def on_comm(self):
-        return torch.cuda.stream(self.comm) if self.cuda else _Null()
+
+def release_buffers():
+    """Frees the persistent exchange buffers (they are re-created by the next call)."""
+    _BUFFERS.clear()
+
+
+def default_head_pieces(local_heads: int, seq: int = 1 << 30, batch: int = 1, limit: int = 8):
+    """Sizes of the pieces the local heads are cut into: as many pieces (at most `limit`) as still leave
+    each about four waves of attention thread blocks (one block per 256 query rows of a head, 148 SMs),
+    the smaller pieces first -- the first piece's exchange is the one nothing hides.  75 600 tokens:
+    5 heads -> [2, 3], 10 -> [2] * 5, 20 -> [2, 2, 2, 2, 3, 3, 3, 3]."""
+    blocks_per_head = batch * ((seq + 255) // 256)
+    min_heads = max(1, -(-4 * 148 // blocks_per_head))
+    pieces = max(1, min(limit, local_heads // min_heads))
+    base, extra = divmod(local_heads, pieces)
+    return [base] * (pieces - extra) + [base + 1] * extra
+
+
+def default_head_chunks(local_heads: int, seq: int = 1 << 30, batch: int = 1, limit: int = 8) -> int:
+    """Number of pieces `default_head_pieces` cuts the local heads into."""
+    return len(default_head_pieces(local_heads, seq, batch, limit))
+
+
+def _piece_sizes(head_chunks, n_loc, seq, batch):
+    if head_chunks is None:
+        return default_head_pieces(n_loc, seq, batch)
+    if isinstance(head_chunks, int):
+        if head_chunks < 1 or n_loc % head_chunks:
+            raise ParametersInvalid(f"head_chunks={head_chunks} must divide the {n_loc} local heads.")
+        return [n_loc // head_chunks] * head_chunks
+    sizes = [int(x) for x in head_chunks]
+    if not sizes or min(sizes) < 1 or sum(sizes) != n_loc:
+        raise ParametersInvalid(f"head_chunks={sizes} must be positive piece sizes adding up to the {n_loc} local heads.")
+    return sizes
+
+
+class _Timer:
+    """CUDA-event stopwatch of the phases of one call; inert unless a `profile` dict was passed."""
+
+    def __init__(self, profile, cuda):
+        self.on = profile is not None and cuda
+        self.profile = profile
+        self.spans = []
+
+    def span(self, name, stream):
+        return _Span(self, name, stream) if self.on else _NULL
+
+    def finish(self):
+        if not self.on:
+            return
+        torch.cuda.synchronize()
+        for name, e0, e1 in self.spans:
+            self.profile[name] = self.profile.get(name, 0.0) + e0.elapsed_time(e1)
+
+
+class _Span:
+    def __init__(self, timer, name, stream):
+        self.timer, self.name, self.stream = timer, name, stream
+
+    def __enter__(self):
+        self.e0 = torch.cuda.Event(enable_timing=True)
+        self.e0.record(self.stream)
+
+    def __exit__(self, *exc):
+        e1 = torch.cuda.Event(enable_timing=True)
+        e1.record(self.stream)
+        self.timer.spans.append((self.name, self.e0, e1))
+        return False
 
 
 class _Null:
@@ -61,111 +136,171 @@ class _Null:
         return False
 
 
-_COMM_STREAMS = {}
+_NULL = _Null()
 
 
-def _comm_stream(device):
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
-    if key not in _COMM_STREAMS:
-        _COMM_STREAMS[key] = torch.cuda.Stream(device=device)
-    return _COMM_STREAMS[key]
-
-
-def default_head_chunks(local_heads: int, seq: int = 1 << 30, batch: int = 1, limit: int = 8) -> int:
-    """Most pieces (a divisor of the local head count, at most `limit`) such that a piece still launches
-    about eight full waves of attention thread blocks (one block per 256 query rows of a head, 148 SMs).
-    A piece of one or two waves loses more to the exchange kernels that run beside it, which take SMs
-    for a while, and to the partial last wave than its overlap wins back: at 75 600 tokens and 8 GPUs
-    (5 local heads) one piece measured 13.8 ms per layer, five pieces 15.4 ms."""
-    blocks_per_head = batch * ((seq + 255) // 256)
-    min_heads = max(1, -(-8 * 148 // blocks_per_head))
-    ok = [c for c in range(1, min(local_heads, limit) + 1) if local_heads % c == 0 and local_heads // c >= min_heads]
-    return max(ok) if ok else 1
+def _move(tensors, table, rows, world, n_loc, head0, heads, inverse=False, rope=None, thread_blocks=0):
+    """mindiesd_ulysses_move on CUDA tensors.  `tensors`: [rows, N, D] views; `table`: [P, rows, k*heads, D]
+    buffer whose chunk r is rank r's side.  Host tensors (the gloo tests of the host logic) take the
+    same movement as torch indexing."""
+    t0 = tensors[0]
+    if t0.is_cuda:
+        from .. import _cabi
+        ptrs = [table[r].data_ptr() for r in range(world)]
+        cos = sin = None
+        mode = 0
+        if rope is not None and not inverse:
+            cos, sin, mode = rope
+        _cabi.ulysses_move(tensors, ptrs, table.stride(1), rows, world, n_loc, head0, heads, inverse=inverse,
+                           cos=cos, sin=sin, rope_mode=mode, thread_blocks=thread_blocks)
+        return
+    if rope is not None:
+        raise ParametersInvalid("The rotary embedding inside the exchange needs CUDA tensors.")
+    d = t0.shape[-1]
+    if not inverse:
+        for i, t in enumerate(tensors):
+            src = t.reshape(rows, world, n_loc, d)[:, :, head0:head0 + heads]  # [rows, P, heads, D]
+            table[:, :, i * heads:(i + 1) * heads].copy_(src.permute(1, 0, 2, 3))
+    else:
+        dst = t0.reshape(rows, world, n_loc, d)[:, :, head0:head0 + heads]
+        dst.copy_(table.permute(1, 0, 2, 3))
 
 
 def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, group=None,
-                      scale: Optional[float] = None, head_chunks: Optional[int] = None,
-                      attn_fn: Optional[Callable] = None) -> torch.Tensor:
+                      scale: Optional[float] = None, head_chunks: Union[None, int, Sequence[int]] = None,
+                      attn_fn: Optional[Callable] = None, rope=None, profile: Optional[dict] = None) -> torch.Tensor:
     """query/key/value: this rank's [B, S/P, N, D] slice (BSND).  Returns this rank's [B, S/P, N, D]
     slice of the attention output over the full sequence.
 
-    head_chunks: pieces the N/P local heads are cut into for overlap (default: default_head_chunks --
-    as many as still leave every piece about eight waves of thread blocks, at most 8).  attn_fn(q, k, v, scale) -> out on [B, S, h, D] BSND tensors replaces the local
-    attention (sparse or FP8 variants); the default is the dense kernel.
+    head_chunks: how the N/P local heads are cut into pieces for overlap: a count (equal pieces), a list of
+    piece sizes, or None for `default_head_pieces`.
+    attn_fn(q, k, v, scale) -> out on [B, S, h, D] BSND tensors replaces the local attention (sparse or
+    FP8 variants); the default is the dense kernel.
+    rope: (cos, sin, rotated_mode) -- fp32 tables [S/P, D] for this rank's tokens and "rotated_half" or
+    "rotated_interleaved": q and k are rotated as `rotary_position_embedding` would, inside the kernel that
+    re-shards them, so the rotated tensors are never written on this rank.
+    profile: a dict that receives the summed CUDA-event milliseconds of the phases of this call
+    ("pack", "exchange_in", "attention", "exchange_out", "unpack"); it synchronises the device.
     """
     if query.dim() != 4 or key.shape != query.shape or value.shape != query.shape:
         raise ParametersInvalid("ulysses_attention expects q, k, v of one shape [B, S/P, N, D].")
     world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
     b, s_loc, n, d = query.shape
     if n % world:
         raise ParametersInvalid(f"The head number {n} must be divisible by the sequence-parallel size {world}.")
     if scale is None:
         scale = d ** -0.5
-    attn = attn_fn or _default_attention
+    rope_args = None
+    if rope is not None:
+        cos, sin, mode = rope
+        if mode not in _ROPE_MODES:
+            raise ParametersInvalid(f"Unsupported rotated_mode: {mode}.")
+        if cos.shape != (b * s_loc, d) and cos.shape != (s_loc, d) or sin.shape != cos.shape or cos.dtype != torch.float32:
+            raise ParametersInvalid("rope tables must be fp32 [S/P, D] for this rank's tokens.")
+        if b > 1 and cos.shape[0] == s_loc:
+            cos, sin = cos.repeat(b, 1), sin.repeat(b, 1)
+        rope_args = (cos.contiguous(), sin.contiguous(), _ROPE_MODES[mode])
     if world == 1:
-        return attn(query, key, value, scale)
+        if rope_args is not None:
+            from ..layers.rope import rotary_position_embedding
+            query, key = (rotary_position_embedding(x, rope[0], rope[1], rope[2], head_first=False) for x in (query, key))
+        return attn_fn(query, key, value, scale) if attn_fn else _default_attention(query, key, value, scale)
     n_loc = n // world
-    if head_chunks is None:
-        head_chunks = default_head_chunks(n_loc, s_loc * world, b)
-    if head_chunks < 1 or n_loc % head_chunks:
-        raise ParametersInvalid(f"head_chunks={head_chunks} must divide the {n_loc} local heads.")
-    hc = n_loc // head_chunks
-    st = _Streams(query.device)
-    out = torch.empty_like(query)
-    # [B, S/P, P, N/P, D]: axis 2 is the destination rank of a head group.
-    qv, kv, vv = (x.view(b, s_loc, world, n_loc, d) for x in (query, key, value))
-    ov = out.view(b, s_loc, world, n_loc, d)
+    sizes = _piece_sizes(head_chunks, n_loc, s_loc * world, b)
+    cuda = query.is_cuda
+    device = query.device
+    q, k, v = (x if x.is_contiguous() else x.contiguous() for x in (query, key, value))
+    rows = b * s_loc
+    qr, kr, vr = (x.view(rows, n, d) for x in (q, k, v))
+    out = torch.empty_like(q)
+    outr = out.view(rows, n, d)
 
-    def exchange_in(c):
-        """Pack chunk c of every destination's head group and start its all-to-all."""
-        send = torch.empty(world, b, s_loc, 3 * hc, d, dtype=query.dtype, device=query.device)
-        for i, x in enumerate((qv, kv, vv)):
-            send[:, :, :, i * hc:(i + 1) * hc].copy_(x[:, :, :, c * hc:(c + 1) * hc].permute(2, 0, 1, 3, 4))
-        recv = torch.empty_like(send)
-        st.comm_after_compute()
-        with st.on_comm():
-            dist.all_to_all_single(recv, send, group=group)
-        if st.cuda:
-            send.record_stream(st.comm)
-            recv.record_stream(st.comm)
-        return recv, st.compute_after_comm()
+    # One set of buffers per piece: a piece's buffers are free again when the call returns.
+    shapes = []
+    for h in sizes:
+        shapes += [(world, rows, 3 * h, d)] * 2 + [(world, rows, h, d)] * 2  # send, recv, o_send, o_recv
+    key_ = (device, q.dtype, world, b, s_loc, n, d, tuple(sizes), id(group))
+    bufs = _buffers(key_, shapes, q.dtype, device)
 
-    def local_attention(recv):
-        # recv[r] holds rank r's rows: with B == 1 the buffer already is [S, 3*hc, D].
+    compute = comm = None
+    if cuda:
+        compute = torch.cuda.current_stream(device)
+        comm = _comm_stream(device)
+        comm.wait_stream(compute)  # the inputs and the buffers' previous readers
+    timer = _Timer(profile, cuda)
+
+    def on_comm():
+        return torch.cuda.stream(comm) if cuda else _NULL
+
+    def record(stream):
+        if not cuda:
+            return None
+        ev = torch.cuda.Event()
+        ev.record(stream)
+        return ev
+
+    def exchange_in(c, head0):
+        """Pack piece c for every destination and start its all-to-all (communication stream)."""
+        send, recv = bufs[4 * c], bufs[4 * c + 1]
+        with on_comm():
+            with timer.span("pack", comm):
+                _move((qr, kr, vr), send, rows, world, n_loc, head0, sizes[c], rope=rope_args,
+                      thread_blocks=0 if c == 0 else 32)
+            with timer.span("exchange_in", comm):
+                dist.all_to_all_single(recv, send, group=group)
+            return record(comm)
+
+    def local_attention(c):
+        h = sizes[c]
+        recv, o_send = bufs[4 * c + 1], bufs[4 * c + 2]
+        # recv[r] holds rank r's rows: with B == 1 the buffer already is [S, 3h, D].
         if b == 1:
-            full = recv.view(1, world * s_loc, 3 * hc, d)
+            full = recv.view(1, world * s_loc, 3 * h, d)
+            o_view = o_send.view(1, world * s_loc, h, d)
         else:
-            full = recv.permute(1, 0, 2, 3, 4).reshape(b, world * s_loc, 3 * hc, d)
-        o = attn(full[:, :, 0:hc], full[:, :, hc:2 * hc], full[:, :, 2 * hc:3 * hc], scale)  # [B, S, hc, D]
-        return o.reshape(b, world, s_loc, hc, d).permute(1, 0, 2, 3, 4).contiguous()  # [P, B, S/P, hc, D]
+            full = recv.view(world, b, s_loc, 3 * h, d).permute(1, 0, 2, 3, 4).reshape(b, world * s_loc, 3 * h, d)
+            o_view = None
+        qq, kk, vv = full[:, :, 0:h], full[:, :, h:2 * h], full[:, :, 2 * h:3 * h]
+        with timer.span("attention", compute):
+            if attn_fn is None and o_view is not None and cuda:
+                _default_attention(qq, kk, vv, scale, out=o_view)  # straight into the return exchange's send buffer
+            else:
+                o = attn_fn(qq, kk, vv, scale) if attn_fn else _default_attention(qq, kk, vv, scale)  # [B, S, h, D]
+                o_send.view(world, b, s_loc, h, d).copy_(o.reshape(b, world, s_loc, h, d).permute(1, 0, 2, 3, 4))
 
-    def exchange_out(o_send):
-        recv = torch.empty_like(o_send)
-        st.comm_after_compute()
-        with st.on_comm():
-            dist.all_to_all_single(recv, o_send, group=group)
-        if st.cuda:
-            o_send.record_stream(st.comm)
-            recv.record_stream(st.comm)
-        return recv, st.compute_after_comm()
+    def exchange_out(c):
+        o_send, o_recv = bufs[4 * c + 2], bufs[4 * c + 3]
+        if cuda:
+            comm.wait_event(record(compute))
+        with on_comm():
+            with timer.span("exchange_out", comm):
+                dist.all_to_all_single(o_recv, o_send, group=group)
+            return record(comm)
 
-    def unpack(c, recv, ev):
-        st.wait(ev)
-        ov[:, :, :, c * hc:(c + 1) * hc].copy_(recv.permute(1, 2, 0, 3, 4))  # recv[p]: heads of rank p's group
+    def unpack(c, head0, ev):
+        if cuda:
+            compute.wait_event(ev)
+        with timer.span("unpack", compute):
+            _move((outr,), bufs[4 * c + 3], rows, world, n_loc, head0, sizes[c], inverse=True)
 
-    pending_in = exchange_in(0)
-    pending_out = None
-    for c in range(head_chunks):
-        recv, ev = pending_in
-        if c + 1 < head_chunks:
-            pending_in = exchange_in(c + 1)
-        st.wait(ev)
-        o_send = local_attention(recv)
-        if pending_out is not None:
-            unpack(*pending_out)
-        r, e = exchange_out(o_send)
-        pending_out = (c, r, e)
-    unpack(*pending_out)
-    del rank
+    head0 = [sum(sizes[:c]) for c in range(len(sizes))]
+    arrived = exchange_in(0, head0[0])
+    returning = None
+    for c in range(len(sizes)):
+        ready = arrived
+        if c + 1 < len(sizes):
+            arrived = exchange_in(c + 1, head0[c + 1])
+        if cuda:
+            compute.wait_event(ready)
+        local_attention(c)
+        if returning is not None:
+            unpack(*returning)
+        returning = (c, head0[c], exchange_out(c))
+    unpack(*returning)
+    if cuda:
+        # The communication stream's last readers of q, k, v are the pack kernels, all of which the
+        # compute stream has waited for; the buffers are only touched again by the next call, which
+        # orders itself behind this one on both streams.
+        comm.wait_stream(compute)
+    timer.finish()
     return out

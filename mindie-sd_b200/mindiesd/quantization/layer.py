@@ -6,6 +6,7 @@ import torch
 from torch import nn
 
 from ..layers.quant.block_quant import fa_block_quant_preprocess, fa_channel_quant_preprocess
+from ..utils.exception import ParametersInvalid
 
 
 def get_quant_weight(weights, name):
@@ -27,6 +28,12 @@ class FP8RotateQuantFA(nn.Module):
         self.register_buffer("q_rot", get_quant_weight(weights, f"{prefix}.q_rot"), persistent=False)
         self.register_buffer("k_rot", get_quant_weight(weights, f"{prefix}.k_rot"), persistent=False)
         self.v_per_channel = v_per_channel
+        if (self.q_rot is None) != (self.k_rot is None):
+            # q k^T is only preserved when both operands are rotated by matching matrices; the
+            # reference fails in its first matmul when one of them is missing (layer.py:284-285).
+            missing = "k_rot" if self.k_rot is None else "q_rot"
+            raise ParametersInvalid(f"FP8RotateQuantFA needs both {prefix}.q_rot and {prefix}.k_rot, or neither "
+                                    f"(fixed Hadamard rotation); {prefix}.{missing} is missing.")
 
     def forward(self, query, key, value, **kwargs):
         layout = kwargs.get("layout", "BNSD")

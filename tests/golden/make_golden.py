@@ -1,10 +1,12 @@
 """Generates the fixtures in this directory by running MindIE-SD's own Python code on CPU.
 
-    python tests/golden/make_golden.py /path/to/MindIE-SD
+    python tests/golden/make_golden.py /path/to/MindIE-SD [rope]
+
+(`rope` regenerates only the rotary-embedding fixture.)
 
 The reference is imported with `torch_npu` replaced by a mock, exactly as its own CPU test runner
 does (tests/run.py:29-41 of MindIE-SD); only its pure-torch functions are called:
-attention_forward(fused=False), avgpool, rearrange_with_remaining, inv_rearrange_with_remaining,
+attention_forward(fused=False), rotary_position_embedding(fused=False), avgpool, rearrange_with_remaining, inv_rearrange_with_remaining,
 do_tensor_rearrange_pooling, get_blockwise_mask, get_mask_index, and the numpy goldens of its plugin tests
 (tests/plugin/test_block_sparse_attention.py, test_sparseblockestimate.py,
 test_adablocksparseattention.py).  Masks are stored bit-packed.
@@ -46,9 +48,34 @@ def import_reference(root):
     return rf, attention_forward, mods
 
 
+ROPE_CASES = [
+    # (name, shape of x, head_first, table shape, table dtype, x dtype, mode, seed)
+    ("half_bsnd_fp32tab", (2, 37, 3, 128), False, (37, 128), torch.float32, torch.bfloat16, "rotated_half", 61),
+    ("inter_bnsd_fp32tab", (1, 2, 50, 128), True, (1, 1, 50, 128), torch.float32, torch.bfloat16, "rotated_interleaved", 62),
+    ("half_bsnd_fp16", (2, 64, 8, 16), False, (1, 64, 1, 16), torch.float32, torch.float16, "rotated_half", 63),
+    ("inter_bsnd_bf16tab", (1, 33, 2, 64), False, (1, 33, 1, 64), torch.bfloat16, torch.bfloat16, "rotated_interleaved", 64),
+    ("half_sbnd_fp32", (20, 2, 3, 32), False, (20, 1, 1, 32), torch.float32, torch.float32, "rotated_half", 65),
+]
+
+
+def make_rope(root):
+    """rotary_position_embedding(fused=False) of the reference on seeded inputs."""
+    import_reference(root)
+    from mindiesd.layers.rope import rotary_position_embedding
+    out = {}
+    for name, xs, head_first, ts, tdt, xdt, mode, seed in ROPE_CASES:
+        x = inputs.randn(seed, *xs, dtype=xdt)
+        cos, sin = inputs.randn(seed + 100, *ts, dtype=tdt), inputs.randn(seed + 200, *ts, dtype=tdt)
+        y = rotary_position_embedding(x, cos, sin, mode, head_first, False)
+        assert y.dtype == xdt
+        out[name] = y.float().numpy()
+    np.savez_compressed(HERE / "rope.npz", **out)
+
+
 def main(root):
     rf, attention_forward, (bsa, est, ada) = import_reference(root)
     torch.set_num_threads(8)
+    make_rope(root)
 
     # 1. permutations: the reference applied to a tensor whose value is its own token index
     perm = {}
@@ -147,4 +174,9 @@ def main(root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) not in (2, 3) or (len(sys.argv) == 3 and sys.argv[2] != "rope"):
+        raise SystemExit("usage: python tests/golden/make_golden.py <path of a MindIE-SD source tree> [rope]")
+    if len(sys.argv) == 3:
+        make_rope(sys.argv[1])
+    else:
+        main(sys.argv[1])

@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in include/mindiesd_b200.h but not exported"
     lib.mindiesd_abi_version.restype = ctypes.c_int
-    assert lib.mindiesd_abi_version() == 1
+    assert lib.mindiesd_abi_version() == 2
 
 
 def test_struct_layouts_match_the_header(tmp_path):

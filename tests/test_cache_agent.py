@@ -70,3 +70,16 @@ def test_default_host_chunks():
     assert default_host_chunks(12, 32760) == 4    # 128 thread blocks per head: three heads per chunk
     assert default_host_chunks(2, 300) == 1
     assert default_host_chunks(7, 1 << 20) == 7
+
+
+def test_fp8_hook_rejects_a_single_rotation_matrix():
+    """q k^T survives the rotation only if both operands are rotated: a checkpoint that lacks one of the
+    two matrices is an error, as it is in MindIE-SD (its matmul receives None, quantization/layer.py:284-285)."""
+    import torch
+    from mindiesd import FP8RotateQuantFA
+    rot = torch.eye(128)
+    FP8RotateQuantFA("blk", {"blk.q_rot": rot, "blk.k_rot": rot})
+    FP8RotateQuantFA("blk", {})
+    for name in ("q_rot", "k_rot"):
+        with pytest.raises(ParametersInvalid):
+            FP8RotateQuantFA("blk", {f"blk.{name}": rot})

@@ -149,9 +149,16 @@ def test_ada_attention_matches_reference_vectors():
         query=qb, key=kb, value=vb, sparse_mask=mask, sparse_count_table=sct, input_layout="BSND", sparse_size=128,
         num_heads=2, num_key_value_heads=2, scale_value=128 ** -0.5, causal=False)
     assert torch.equal(out_b.transpose(1, 2), out)
-    with pytest.raises(RuntimeError):
-        torch.ops.mindiesd.ada_block_sparse_attention(
-            query=q.cuda(), key=k.cuda(), value=v.cuda(), sparse_mask=mask, sparse_count_table=sct, causal=True)
+    # causal=True (the schema's default): the token-level triangle inside the kept blocks, which is what the
+    # golden's in-block triangle (tests/plugin/test_adablocksparseattention.py:69-72) amounts to for a
+    # lower-triangular mask that keeps the diagonal blocks
+    tri = torch.tril(torch.ones(1, 2, 3, 3, dtype=torch.int8)).cuda()
+    out_c = torch.ops.mindiesd.ada_block_sparse_attention(
+        query=q.cuda(), key=k.cuda(), value=v.cuda(), sparse_mask=tri, sparse_count_table=tri.sum(-1, dtype=torch.int32),
+        input_layout="BNSD", sparse_size=128, num_heads=2, num_key_value_heads=2, scale_value=128 ** -0.5, causal=True)
+    keep = torch.tril(torch.ones(300, 300, dtype=torch.bool))
+    want_c = oa.attention_math(q, k, v, attn_mask=keep, head_first=True)
+    assert (out_c.cpu().float() - want_c.float()).abs().max().item() <= 2e-2
 
 
 @pytest.mark.parametrize("layout", ["BNSD", "BSND"])

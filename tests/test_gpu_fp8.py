@@ -35,7 +35,8 @@ def test_channel_quant_matches_oracle():
 
 
 def test_rotated_block_quant_close_to_oracle():
-    """The in-kernel butterfly and the oracle's matrix product round differently, so the comparison
+    """The kernel's tensor-core product with the +-1 matrix (1/sqrt(128) folded into the scale) and the
+    oracle's fp32 matrix product round differently, so the comparison
     is on dequantised values: within one e4m3 step (2^-3 relative) of the oracle's."""
     from mindiesd import _cabi
     x = inputs.randn(95, 1, 2, 600, 128, dtype=torch.bfloat16)

@@ -156,3 +156,16 @@ def test_temporal_band_extension():
     assert band.shape == (8, 8)
     assert band[0, 3] and not band[0, 4] and band[7, 4] and not band[7, 3]
     assert np.array_equal(band, band.T)
+
+
+def test_rope_oracle_matches_reference_vectors():
+    """oracle.rope against rotary_position_embedding(fused=False) of the reference (rope.npz)."""
+    import make_golden
+    from oracle import rope as orope
+    z = np.load(G / "rope.npz")
+    for name, xs, head_first, ts, tdt, xdt, mode, seed in make_golden.ROPE_CASES:
+        x = inputs.randn(seed, *xs, dtype=xdt)
+        cos, sin = inputs.randn(seed + 100, *ts, dtype=tdt), inputs.randn(seed + 200, *ts, dtype=tdt)
+        got = orope.rotary_position_embedding(x, cos, sin, mode, head_first)
+        assert got.dtype == xdt
+        assert torch.equal(got.float(), torch.from_numpy(z[name])), name

@@ -43,7 +43,8 @@ def _worker(rank, world, port, head_chunks, batch, result):
         out = ulysses_attention(shard(q), shard(k), shard(v), scale=d ** -0.5, head_chunks=head_chunks, attn_fn=attn)
         want = oa.attention_math(q, k, v, scale=d ** -0.5, head_first=False)
         ok = torch.allclose(out, shard(want), atol=1e-5)
-        ok = ok and len(calls) == head_chunks and calls[0] == (batch, s, n // world // head_chunks, d)
+        sizes = [n // world // head_chunks] * head_chunks if isinstance(head_chunks, int) else list(head_chunks)
+        ok = ok and [c[2] for c in calls] == sizes and calls[0] == (batch, s, sizes[0], d)
         # the re-shard itself against the single-process restatement
         shards = [x.contiguous() for x in q.chunk(world, dim=1)]
         full = ou.seq_to_head(shards)[rank]
@@ -54,7 +55,7 @@ def _worker(rank, world, port, head_chunks, batch, result):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,head_chunks,batch", [(2, 1, 1), (2, 4, 1), (4, 2, 1), (2, 2, 2)])
+@pytest.mark.parametrize("world,head_chunks,batch", [(2, 1, 1), (2, 4, 1), (4, 2, 1), (2, 2, 2), (2, (1, 3), 1)])
 def test_ulysses_matches_single_process(world, head_chunks, batch):
     ctx = mp.get_context("spawn")
     result = ctx.Manager().dict()
@@ -83,11 +84,12 @@ def test_ulysses_rejects_indivisible_heads():
         dist.destroy_process_group()
 
 
-def test_default_head_chunks_keeps_pieces_large():
-    from mindiesd.parallel import default_head_chunks
-    # 75 600 tokens: 296 thread blocks per head, so a piece needs four heads for eight waves
-    assert default_head_chunks(5, 75600) == 1     # 8 GPUs
-    assert default_head_chunks(10, 75600) == 2    # 4 GPUs
-    assert default_head_chunks(20, 75600) == 5    # 2 GPUs
-    assert default_head_chunks(20, 4096) == 1     # short sequences: never below eight waves
-    assert default_head_chunks(12) == 6 and default_head_chunks(7) == 7  # length unknown: the largest divisor up to 8
+def test_default_head_pieces_keeps_pieces_large_and_the_first_small():
+    from mindiesd.parallel import default_head_chunks, default_head_pieces
+    # 75 600 tokens: 296 thread blocks per head, so a piece needs two heads for four waves
+    assert default_head_pieces(5, 75600) == [2, 3]            # 8 GPUs: uneven pieces, the smaller first
+    assert default_head_pieces(10, 75600) == [2] * 5          # 4 GPUs
+    assert default_head_pieces(20, 75600) == [2, 2, 2, 2, 3, 3, 3, 3]  # 2 GPUs: at most eight pieces
+    assert default_head_pieces(20, 4096) == [20]              # short sequences: one piece
+    assert default_head_pieces(12) == [1, 1, 1, 1, 2, 2, 2, 2]  # length unknown
+    assert default_head_chunks(5, 75600) == 2 and default_head_chunks(20, 4096) == 1
