@@ -156,10 +156,25 @@ def cpu_attention_sample(seq, target_seconds=12.0, repeats=1):
             "sample": f"1 head x {rows} query rows x {seq} keys, fp32 on bf16-rounded values, {best:.2f} s"}, best, flops
 
 
+WORKLOAD = "wan2.1-14b-720p dense self-attention, B1 N40 S75600 D128 (21x45x80 latent grid)"
+
+
+def use_all_host_cores():
+    """torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU legs are meant to use the cores the
+    process may run on."""
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    torch.set_num_threads(max(1, cores))
+    return torch.get_num_threads()
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    use_all_host_cores()
     seq = 75600
     times, flops = [], 0.0
     info = None
@@ -174,7 +189,7 @@ def run_reference_arm(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * 75600.0 * 75600 * 40 * 4 * HEAD_DIM / (value * 1e12),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "wan2.1-14b-720p dense self-attention, B1 N40 S75600 D128",
+        "config": {"workload": WORKLOAD,
                    "note": "CPU oracle (the reference's unfused torch formula) on the host cores; each step is a "
                            "bounded sample; ms_per_step is the full layer extrapolated by FLOPs"},
         "cpu_baseline": info,
@@ -187,9 +202,24 @@ def run_reference_arm(args):
 # ---------------------------------------------------------------------------------------------------
 # GPU workloads
 # ---------------------------------------------------------------------------------------------------
+def ulysses_parity(q_full, k_full, v_full, step_out, rank, world, heads_checked):
+    """The sequence-parallel result against the single-GPU kernel on the same seeded tensors: this rank
+    runs the dense kernel on whole heads of the UNSHARDED q, k, v (it generated them) and requires its
+    rows of those heads to be bit-equal in the Ulysses output.  Same kernel, same tiles, same order of
+    key blocks: any difference is an error of the exchange."""
+    from mindiesd import _cabi
+    s_loc = q_full.shape[1] // world
+    rows = slice(rank * s_loc, (rank + 1) * s_loc)
+    equal = True
+    for h in heads_checked:
+        want = _cabi.attention(q_full[:, :, h:h + 1], k_full[:, :, h:h + 1], v_full[:, :, h:h + 1], head_first=False)
+        equal = equal and torch.equal(step_out[:, :, h], want[:, rows, 0])
+    return equal
+
+
 def dense_or_ulysses(args, rank, world, device):
     import workloads
-    from mindiesd import _cabi, attention_forward, ulysses_attention
+    from mindiesd import _cabi, ulysses_attention
     import torch.distributed as dist
 
     cfg = workloads.C3
@@ -197,47 +227,89 @@ def dense_or_ulysses(args, rank, world, device):
         cfg = workloads.Config(cfg.name, cfg.batch, args.heads, cfg.grid, cfg.seq, cfg.dtype)
     q, k, v = workloads.make_qkv(cfg, device, seed=0, layout="BSND")  # [1, S, 40, 128]
     s_loc = cfg.seq // world
-    if world > 1:
-        q, k, v = (x[:, rank * s_loc:(rank + 1) * s_loc].contiguous() for x in (q, k, v))
-    torch.cuda.empty_cache()
     barrier = (lambda: dist.barrier()) if world > 1 else None
-    launches_per_step = 1
+    parity = None
+    pieces = None
+    if world > 1:
+        from mindiesd.parallel import default_head_pieces
+        if args.ulysses_chunks:
+            pieces = [cfg.heads // world // args.ulysses_chunks] * args.ulysses_chunks
+        else:
+            pieces = default_head_pieces(cfg.heads // world, cfg.seq)
+        qs, ks, vs = (x[:, rank * s_loc:(rank + 1) * s_loc].contiguous() for x in (q, k, v))
+        checked = sorted({0, cfg.heads // 2 + 1, cfg.heads - 1})  # heads of the first, a middle and the last rank
+        ok = ulysses_parity(q, k, v, ulysses_attention(qs, ks, vs, head_chunks=pieces), rank, world, checked)
+        flag = torch.tensor([1 if ok else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        parity = {"heads": checked, "equal": bool(flag.item()), "against": "single-GPU kernel on the unsharded tensors, torch.equal, every rank"}
+        if not parity["equal"]:
+            raise SystemExit(f"rank {rank}: the sequence-parallel output differs from the single-GPU kernel")
+        del q, k, v
+        q, k, v = qs, ks, vs
+    torch.cuda.empty_cache()
+    launches_per_layer = 1 if world == 1 else 3 * len(pieces)
     if world == 1:
         out = torch.empty_like(q)
-        step = lambda: _cabi.attention(q, k, v, head_first=False, out=out)  # noqa: E731
+        layer = lambda: _cabi.attention(q, k, v, head_first=False, out=out)  # noqa: E731
     else:
-        from mindiesd.parallel import default_head_chunks
-        chunks = args.ulysses_chunks or default_head_chunks(cfg.heads // world, cfg.seq)
-        launches_per_step = chunks
-        step = lambda: ulysses_attention(q, k, v, head_chunks=chunks)  # noqa: E731
+        layer = lambda: ulysses_attention(q, k, v, head_chunks=pieces)  # noqa: E731
+
+    # The timed region should last about two seconds at every GPU count, so that every N runs in the
+    # same power state (a short region finishes before the power cap engages): a step repeats the
+    # layer `layers` times.
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    layer()
+    torch.cuda.synchronize()
+    e0.record()
+    layer()
+    e1.record()
+    torch.cuda.synchronize()
+    probe = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(probe, op=dist.ReduceOp.MAX)
+    layers = 1 if args.layers_per_step == 0 and world == 1 else (
+        args.layers_per_step or max(1, round(2000.0 / (probe.item() * args.steps))))
+
+    def step():
+        for _ in range(layers):
+            layer()
 
     sampler = ClockSampler(physical_gpu_index(device.index))
     sampler.start()
     ms = timed(step, args.steps, args.warmup, barrier)
     clocks = sampler.stop()
 
+    phases = None
+    if world > 1:  # one more, untimed, call with CUDA events around each phase
+        prof = {}
+        ulysses_attention(q, k, v, head_chunks=pieces, profile=prof)
+        t = torch.tensor([prof.get(n, 0.0) for n in ("pack", "exchange_in", "attention", "exchange_out", "unpack")],
+                         dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        phases = dict(zip(("pack_ms", "exchange_in_ms", "attention_ms", "exchange_out_ms", "unpack_ms"),
+                          (round(x, 4) for x in t.tolist())))
+
     # End to end through the public Python API with host buffers: every step copies this rank's
-    # q, k, v from pinned host memory and reads its output back.  On one GPU the public
-    # attention_forward_host pipelines the copies with the kernel, head chunk by head chunk.
+    # q, k, v from pinned host memory and reads its output back, copies pipelined with the kernels.
+    from mindiesd import attention_forward_host
+    from mindiesd.layers.flash_attn.host_io import default_host_chunks
+    e2e_chunks = None
     if world == 1:
         hq, hk, hv = (torch.empty(x.transpose(1, 2).shape, dtype=x.dtype, pin_memory=True).copy_(x.transpose(1, 2))
                       for x in (q, k, v))  # head-first pinned copies
+        e2e_chunks = args.e2e_chunks if args.e2e_chunks and cfg.heads % args.e2e_chunks == 0 else default_host_chunks(cfg.heads, cfg.seq)
     else:
         hq, hk, hv = (torch.empty(x.shape, dtype=x.dtype, pin_memory=True).copy_(x) for x in (q, k, v))
     ho = torch.empty(hq.shape, dtype=q.dtype, pin_memory=True)
-    from mindiesd import attention_forward_host
-    from mindiesd.layers.flash_attn.host_io import default_host_chunks
-    e2e_chunks = args.e2e_chunks if args.e2e_chunks and cfg.heads % args.e2e_chunks == 0 else default_host_chunks(cfg.heads, cfg.seq)
 
     def e2e_step():
         if world == 1:
             attention_forward_host(hq, hk, hv, out=ho, head_chunks=e2e_chunks)
-            return
-        dq, dk, dv = (h.to(device, non_blocking=True) for h in (hq, hk, hv))
-        o = ulysses_attention(dq, dk, dv, head_chunks=launches_per_step)
-        ho.copy_(o, non_blocking=True)
+        else:
+            from mindiesd.parallel import ulysses_attention_host
+            ulysses_attention_host(hq, hk, hv, out=ho, head_chunks=pieces)
 
-    e2e_steps = max(1, min(args.steps, 5))
+    e2e_steps = max(1, args.steps)
     e2e_ms = timed(e2e_step, e2e_steps, 1, barrier) if not args.kernel_only else float("nan")
 
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
@@ -249,23 +321,37 @@ def dense_or_ulysses(args, rank, world, device):
         return None
     peaks = measured_peaks()
     ms_step = ms / args.steps
-    value = cfg.flops / (ms_step * 1e-3) / 1e12
+    ms_layer = ms_step / layers
+    value = cfg.flops / (ms_layer * 1e-3) / 1e12
+    config = {"workload": WORKLOAD if not args.heads else WORKLOAD.replace("N40", f"N{cfg.heads}") + " [heads reduced]",
+              "layout": "BSND",
+              "parallelism": "single GPU" if world == 1 else f"ulysses sp{world}, local heads in pieces of {pieces}",
+              "layers_per_step": layers, "ms_per_layer": ms_layer, "flops_per_layer": cfg.flops,
+              "l2": "operands (3.1 GB per layer) exceed L2; no flush",
+              "tflops_per_gpu": value / world, "kernel_status": status}
+    if clocks.get("sm_mhz"):
+        # time x clock: what the layer costs in SM cycles, comparable across runs at different power states
+        config["ms_per_layer_x_sm_mhz"] = ms_layer * clocks["sm_mhz"]
+    if parity is not None:
+        config["parity"] = parity
+    if phases is not None:
+        exposed = max(0.0, ms_layer - phases["attention_ms"])
+        config["phases_of_one_layer"] = dict(phases, exposed_ms=round(exposed, 4),
+                                             note="CUDA events of one untimed layer, max over ranks; exposed = "
+                                                  "timed ms per layer minus the attention kernels' own time")
     line = {
         "metric": "attention_dense_equiv_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"wan2.1-14b-720p dense self-attention, B1 N{cfg.heads} S75600 D128 (21x45x80 latent grid)",
-                   "layout": "BSND", "parallelism": "single GPU" if world == 1 else f"ulysses sp{world}, {launches_per_step} head chunks",
-                   "flops_per_step": cfg.flops, "l2": "operands (3.1 GB per step) exceed L2; no flush",
-                   "tflops_per_gpu": value / world, "kernel_status": status},
+        "config": config,
         "clocks": clocks,
         "e2e": {"value": cfg.flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": 3 * q.numel() * q.element_size() * world,
                 "d2h_bytes_per_step": q.numel() * q.element_size() * world,
                 "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
                 "api": f"mindiesd.attention_forward_host ({e2e_chunks} head chunks, copies overlapped)" if world == 1
-                       else "mindiesd.ulysses_attention"},
-        "gpu_launches": launches_per_step * args.steps,
+                       else "mindiesd.parallel.ulysses_attention_host (copies pipelined piece by piece)"},
+        "gpu_launches": launches_per_layer * layers * args.steps,
     }
     if world == 1:
         peak = peaks["bf16_tflops_sustained"]
@@ -274,9 +360,37 @@ def dense_or_ulysses(args, rank, world, device):
                             "frac_of_burst": value / peaks["bf16_tflops"], "frac_of_nominal_2250": value / 2250.0,
                             "kernel": "fa_fwd_kernel<bf16>", "flops_per_launch": cfg.flops}
         if not args.kernel_only:
+            use_all_host_cores()
             cpu, _, _ = cpu_attention_sample(cfg.seq, target_seconds=12.0)
             line["cpu_baseline"] = cpu
+            if not args.no_secondary:
+                del q, k, v, out, hq, hk, hv, ho
+                torch.cuda.empty_cache()
+                line["config"]["secondary"] = secondary_lines(args, device, value, clocks)
     return line
+
+
+def secondary_lines(args, device, dense_value, dense_clocks):
+    """The sparse and FP8 workloads of the same shape, measured in the same run as the headline, so that
+    their ratios to the dense kernel are taken on one GPU in one power state."""
+    res = {}
+    for name in ("sparse", "fp8"):
+        sub = argparse.Namespace(**vars(args))
+        sub.workload, sub.steps, sub.warmup, sub.heads = name, max(3, min(args.steps, 10)), 3, 0
+        line = single_gpu_workload(sub, device)
+        entry = {"ms_per_step": line["ms_per_step"], "dense_equiv_tflops": line["value"], "clocks": line["clocks"],
+                 "speedup_over_dense": line["value"] / dense_value}
+        sm, dsm = line["clocks"].get("sm_mhz"), dense_clocks.get("sm_mhz")
+        if sm and dsm:
+            # at equal clocks: ratio of (time x median SM MHz)
+            entry["speedup_over_dense_at_equal_clocks"] = (line["value"] / sm) / (dense_value / dsm)
+        for key in ("block_density", "executed_tflop", "sparsity_arg"):
+            if key in line["config"]:
+                entry[key] = line["config"][key]
+        entry["roofline_frac"] = line["roofline"]["frac"]
+        res[name] = entry
+        torch.cuda.empty_cache()
+    return res
 
 
 def single_gpu_workload(args, device):
@@ -393,6 +507,9 @@ def single_gpu_workload(args, device):
     ms_step = ms / args.steps
     value = work / (ms_step * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
     peak = peaks["bf16_tflops_sustained"] if bound == "tensor" else peaks["hbm_gbs"]
+    # The roofline fraction is of the work actually executed: a block-sparse launch is measured by the
+    # blocks it walks, not by the dense-equivalent figure of the metric.
+    achieved = value * extra["executed_tflop"] * 1e12 / work if "executed_tflop" in extra else value
     return {
         "metric": "attention_dense_equiv_tflops" if unit == "TFLOP/s" else "achieved_hbm_gbs", "value": value,
         "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
@@ -400,7 +517,7 @@ def single_gpu_workload(args, device):
         "dtype": "e4m3" if name in ("fp8", "fp8_layer") else "bf16", "data": "synthetic",
         "config": dict({"workload": label + (f" [heads reduced to {args.heads}]" if args.heads else ""), "l2": "operands exceed L2; no flush", "kernel_status": _cabi.device_status()}, **extra),
         "clocks": clocks,
-        "roofline": {"bound": bound, "achieved": value, "peak": peak, "unit": unit, "frac": value / peak, "traffic": None,
+        "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak, "traffic": None,
                      "peak_source": peaks["source"]},
         "gpu_launches": launches * args.steps,
     }
@@ -420,9 +537,10 @@ def main():
     ap.add_argument("--cdf", type=float, default=0.9, help="cumulative-mass threshold of the ada_bsa estimate")
     ap.add_argument("--heads", type=int, default=0, help="reduced head count for profiler captures (default: the full 40)")
     ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs (profiler captures)")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the sparse and FP8 legs of the headline run")
+    ap.add_argument("--layers-per-step", type=int, default=0,
+                    help="layers one step repeats (0: one on a single GPU, else enough for a timed region of about 2 s)")
     args = ap.parse_args()
-    if args.warmup < 3 and args.impl == "b200":
-        args.warmup = 3
     if args.impl == "reference":
         run_reference_arm(args)
         return

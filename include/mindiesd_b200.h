@@ -424,6 +424,16 @@ typedef struct mindiesd_ulysses_move_args {
 int mindiesd_ulysses_move(const mindiesd_ulysses_move_args* args, void* stream);
 
 /*
+ * Strided copy between pinned host memory and device memory (either direction, chosen by the
+ * addresses) on a stream: `height` rows of `width_bytes`, rows `*_pitch` bytes apart.  It lets a
+ * host-resident [rows, N, D] tensor be brought in one head range at a time, so that the first piece
+ * of a sequence-parallel layer starts before the whole tensor has crossed PCIe.  The reference keeps
+ * activations on the device and has no counterpart.
+ */
+int mindiesd_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                     size_t height, void* stream);
+
+/*
  * Device status word of the current device: 0, or the code of the first bounded wait inside a
  * kernel that gave up since the last call.  Synchronises the device; clears the word.
  */

@@ -41,8 +41,63 @@ int* device_status_word() {
     return words[dev];
 }
 
+namespace {
+// Encoded tensor maps, keyed by everything that goes into them.  A denoising loop calls the same
+// operator on the same buffers every step (and the pipelined host path once per head chunk), so the
+// three driver calls per launch are paid once per buffer.  The map is a pure function of its key;
+// the memory behind the pointer may change freely.
+struct MapKey {
+    const void* base;
+    int64_t channels, tokens, heads, batch, stride[3];
+    int dtype, box_rows, device;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && channels == o.channels && tokens == o.tokens && heads == o.heads && batch == o.batch &&
+               stride[0] == o.stride[0] && stride[1] == o.stride[1] && stride[2] == o.stride[2] && dtype == o.dtype &&
+               box_rows == o.box_rows && device == o.device;
+    }
+};
+constexpr int kMapCacheSize = 128;
+struct MapCache {
+    std::mutex mu;
+    MapKey keys[kMapCacheSize];
+    CUtensorMap maps[kMapCacheSize];
+    bool used[kMapCacheSize] = {};
+    unsigned next = 0;
+};
+MapCache& map_cache() {
+    static MapCache c;
+    return c;
+}
+int encode_tile_map_uncached(CUtensorMap* map, const void* base, int dtype, int64_t channels, int64_t tokens,
+                             int64_t heads, int64_t batch, const int64_t stride[3], int box_rows);
+}  // namespace
+
 int encode_tile_map(CUtensorMap* map, const void* base, int dtype, int64_t channels, int64_t tokens,
                     int64_t heads, int64_t batch, const int64_t stride[3], int box_rows) {
+    MapKey key = {base, channels, tokens, heads, batch, {stride[0], stride[1], stride[2]}, dtype, box_rows, 0};
+    if (cudaGetDevice(&key.device) != cudaSuccess) return MINDIESD_E_DRIVER;
+    MapCache& c = map_cache();
+    {
+        std::lock_guard<std::mutex> lock(c.mu);
+        for (int i = 0; i < kMapCacheSize; ++i)
+            if (c.used[i] && c.keys[i] == key) {
+                *map = c.maps[i];
+                return MINDIESD_OK;
+            }
+    }
+    const int rc = encode_tile_map_uncached(map, base, dtype, channels, tokens, heads, batch, stride, box_rows);
+    if (rc != MINDIESD_OK) return rc;
+    std::lock_guard<std::mutex> lock(c.mu);
+    const unsigned slot = c.next++ % kMapCacheSize;
+    c.keys[slot] = key;
+    c.maps[slot] = *map;
+    c.used[slot] = true;
+    return MINDIESD_OK;
+}
+
+namespace {
+int encode_tile_map_uncached(CUtensorMap* map, const void* base, int dtype, int64_t channels, int64_t tokens,
+                             int64_t heads, int64_t batch, const int64_t stride[3], int box_rows) {
     const int eb = dtype_bytes(dtype);
     if (eb != 1 && eb != 2) return MINDIESD_E_DTYPE;
     EncodeFn fn = encode_fn();
@@ -66,6 +121,7 @@ int encode_tile_map(CUtensorMap* map, const void* base, int dtype, int64_t chann
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? MINDIESD_OK : MINDIESD_E_DRIVER;
 }
+}  // namespace
 
 }  // namespace sdb
 

@@ -18,6 +18,7 @@
 #include "ptx_sm100.cuh"
 
 #include <cuda_bf16.h>
+#include <type_traits>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
@@ -39,6 +40,12 @@ constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
 #ifndef SDB_FA_REGS_OTHER
 #define SDB_FA_REGS_OTHER 64
 #endif
+// Two-byte operands: hand the probabilities of a block to the MMA thread in two halves (keys 0-63, 64-127),
+// so that the first half of the P V product runs under the second half of the exponentials.
+#ifndef SDB_FA_HALVES
+#define SDB_FA_HALVES 0
+#endif
+constexpr bool kHalves = SDB_FA_HALVES != 0;
 constexpr int kRegsSoftmax = SDB_FA_REGS_SOFTMAX;
 constexpr int kRegsOther = SDB_FA_REGS_OTHER;
 static_assert(2 * 128 * kRegsSoftmax + 128 * kRegsOther <= 65536, "register file of one SM");
@@ -112,6 +119,7 @@ __device__ __forceinline__ void poison_row(const FaParams& p, int batch, int hea
 template <int kIn>
 __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_constant__ FaParams p) {
     constexpr bool kFp8 = kIn == 3;
+    constexpr bool kSplit = kFp8 || kHalves;  // P is handed to the MMA thread in two halves
     using C = Cfg<kFp8>;
     extern __shared__ uint8_t smem_raw[];
     // The swizzle pattern of TMA and of the MMA descriptors is a function of the address bits, so
@@ -132,7 +140,10 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     // operands hand a block over whole, on the second barrier.
     auto bar_p = [&](int t, int h) { return bar_base + 8u * (3 + 2 * C::kStages + 2 * t + h); };
     auto bar_done = [&]() { return bar_base + 8u * (7 + 2 * C::kStages); };
-    constexpr int kNumBars = 8 + 2 * C::kStages;
+    // First half of a tile's P V product complete (two-byte operands handing P over in halves): only
+    // waited for on the rare path that must rescale O between the halves.
+    auto bar_h = [&](int t) { return bar_base + 8u * (8 + 2 * C::kStages + t); };
+    constexpr int kNumBars = 10 + 2 * C::kStages;
     static_assert(kNumBars * 8 + 16 <= 256, "barrier area");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -201,6 +212,8 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             mbar_init(bar_p(t, 1), kTile);
         }
         mbar_init(bar_done(), 1);
+        mbar_init(bar_h(0), 1);
+        mbar_init(bar_h(1), 1);
         *abort_flag = 0;
         *abort_site = 0;
         fence_mbar_init();
@@ -371,16 +384,17 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 ok = mbar_wait(bar_full(vslot.idx), vslot.phase, abort_flag, 12, wait_us);
                 if (!ok) break;
                 if (f & 1) {
-                    if constexpr (kFp8) {
+                    if constexpr (kSplit) {
                         ok = mbar_wait(bar_p(0, 0), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13, wait_us);
                         if (!ok) break;
                         tc_fence_after();
                         issue_pv(0, 0, vslot.idx, pv_cnt[0] > 0);
+                        if constexpr (!kFp8) umma_commit(bar_h(0));
                     }
                     ok = mbar_wait(bar_p(0, 1), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13, wait_us);
                     if (!ok) break;
                     tc_fence_after();
-                    if constexpr (!kFp8) issue_pv(0, 0, vslot.idx, pv_cnt[0] > 0);
+                    if constexpr (!kSplit) issue_pv(0, 0, vslot.idx, pv_cnt[0] > 0);
                     issue_pv(0, 1, vslot.idx, true);
                     ++pv_cnt[0];
                 }
@@ -391,16 +405,17 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 }
                 if (nf & 1) issue_s(0, kslot.idx);
                 if (f & 2) {
-                    if constexpr (kFp8) {
+                    if constexpr (kSplit) {
                         ok = mbar_wait(bar_p(1, 0), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14, wait_us);
                         if (!ok) break;
                         tc_fence_after();
                         issue_pv(1, 0, vslot.idx, pv_cnt[1] > 0);
+                        if constexpr (!kFp8) umma_commit(bar_h(1));
                     }
                     ok = mbar_wait(bar_p(1, 1), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14, wait_us);
                     if (!ok) break;
                     tc_fence_after();
-                    if constexpr (!kFp8) issue_pv(1, 0, vslot.idx, pv_cnt[1] > 0);
+                    if constexpr (!kSplit) issue_pv(1, 0, vslot.idx, pv_cnt[1] > 0);
                     issue_pv(1, 1, vslot.idx, true);
                     ++pv_cnt[1];
                 }
@@ -520,7 +535,94 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(mx8[i], __uint_as_float(s[3][i + 24]));
                 return fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             };
-            if constexpr (!kFp8) {
+            if constexpr (!kFp8 && kHalves) {
+                // As below, but in two halves of 64 keys, each tested and handed over by itself, so that the
+                // first half of the P V product runs while the second half's exponentials are taken.  If the
+                // SECOND half fails its test, the first is already with the MMA thread: the row waits for
+                // that half product (bar_h), then rescales O -- which holds it -- and redoes its own half.
+                if (cnt == 0) m_run = fmaxf(row_max() * mult, -3.0e38f);
+                const uint64_t mult2 = pack2(mult, mult);
+                auto rescale_o = [&](float alpha) {
+    #pragma unroll 1
+                    for (int c = 0; c < kHeadDim / 8; ++c) {
+                        uint32_t o[8];
+                        tmem_ld8(taddr_o + c * 8, o);
+                        tmem_wait_ld();
+    #pragma unroll
+                        for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st8(taddr_o + c * 8, o);
+                    }
+                };
+                auto half = [&](auto hconst) -> bool {
+                    constexpr int h = decltype(hconst)::value;
+                    uint32_t pk[2][16];
+                    float sum = 0.0f;
+    #pragma unroll 1
+                    for (int pass = 0; pass < 2; ++pass) {
+                        const float neg_m = -m_run;
+                        const uint64_t negm2 = pack2(neg_m, neg_m);
+                        uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
+    #pragma unroll
+                        for (int cc = 0; cc < 2; ++cc) {
+                            constexpr int base = 2 * h;
+    #pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                float e0, e1, e2, e3;
+                                unpack2(fma2(pack2(__uint_as_float(s[base + cc][4 * i]), __uint_as_float(s[base + cc][4 * i + 1])), mult2, negm2), e0, e1);
+                                e0 = ex2_approx(e0);
+                                e1 = ex2_approx(e1);
+                                unpack2(fma2(pack2(__uint_as_float(s[base + cc][4 * i + 2]), __uint_as_float(s[base + cc][4 * i + 3])), mult2, negm2), e2, e3);
+                                e2 = ex2_approx(e2);
+                                e3 = ex2_approx(e3);
+                                sum2[0] = add2(sum2[0], pack2(e0, e1));
+                                sum2[1] = add2(sum2[1], pack2(e2, e3));
+                                pk[cc][2 * i] = pack_pair(e0, e1, kIn);
+                                pk[cc][2 * i + 1] = pack_pair(e2, e3, kIn);
+                            }
+                        }
+                        {
+                            float a, b;
+                            unpack2(add2(sum2[0], sum2[1]), a, b);
+                            sum = a + b;
+                        }
+                        if (pass == 1 || cnt == 0) break;
+                        if (!__any_sync(0xffffffffu, !(sum <= kRedoSum))) break;
+                        if constexpr (h == 1) {
+                            // the first half's product must be over before O changes
+                            if (!__all_sync(0xffffffffu, mbar_wait(bar_h(t), static_cast<uint32_t>(cnt) & 1u, abort_flag, 24 + t, wait_us)))
+                                return false;
+                            tc_fence_after();
+                        }
+                        // Scores not yet stored over: all of them (first half) or keys 64-127 (second half).
+    #pragma unroll
+                        for (int c = 2 * h; c < 4; ++c) tmem_ld32(taddr_s + c * 32, s[c]);
+                        tmem_wait_ld();
+                        if (masked) mask_scores();
+                        float mx = -INFINITY;
+                        if constexpr (h == 0) {
+                            mx = row_max();
+                        } else {
+    #pragma unroll
+                            for (int i = 0; i < 32; ++i) mx = fmax3(mx, __uint_as_float(s[2][i]), __uint_as_float(s[3][i]));
+                        }
+                        const float m_new = fmaxf(m_run, mx * mult);
+                        const float alpha = ex2_approx(m_run - m_new);
+                        m_run = m_new;
+                        l_run *= alpha;
+                        rescale_o(alpha);
+                    }
+    #pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) tmem_st16(taddr_s + (2 * h + cc) * 16, pk[cc]);
+                    l_run += sum;
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(bar_p(t, h));
+                    return true;
+                };
+                ok = half(std::integral_constant<int, 0>{});
+                if (ok) ok = half(std::integral_constant<int, 1>{});
+                if (!ok) break;
+            } else if constexpr (!kFp8) {
                 // The probabilities are taken against the running max right away and kept in registers; the
                 // scores die as they are consumed.  Every probability is non-negative, so a row sum within
                 // 2^lag bounds each of them: only if that test fails somewhere in the warp -- rare after the

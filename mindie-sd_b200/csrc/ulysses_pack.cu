@@ -302,3 +302,13 @@ extern "C" int mindiesd_rope(const mindiesd_rope_args* a, void* stream) {
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? MINDIESD_OK : static_cast<int>(e);
 }
+
+extern "C" int mindiesd_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                                size_t height, void* stream) {
+    if (!dst || !src) return MINDIESD_E_NULL;
+    if (width_bytes == 0 || height == 0) return MINDIESD_OK;
+    if (width_bytes > dst_pitch || width_bytes > src_pitch) return MINDIESD_E_STRIDE;
+    const cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, height, cudaMemcpyDefault,
+                                            static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? MINDIESD_OK : static_cast<int>(e);
+}

@@ -474,3 +474,11 @@ def ulysses_move(tensors, table_ptrs, table_row_stride, rows, world, group_heads
         a.cos, a.sin, a.rope_mode = cos.data_ptr(), sin.data_ptr(), int(rope_mode)
     a.thread_blocks = int(thread_blocks)
     check(lib().mindiesd_ulysses_move(C.byref(a), current_stream_ptr(t0.device)), "mindiesd_ulysses_move")
+
+
+def copy_2d(dst_ptr, dst_pitch, src_ptr, src_pitch, width_bytes, height, stream):
+    """mindiesd_copy_2d on `stream` (a torch.cuda.Stream): rows of width_bytes, pitches in bytes."""
+    fn = lib().mindiesd_copy_2d
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p]
+    check(fn(dst_ptr, dst_pitch, src_ptr, src_pitch, width_bytes, height, stream.cuda_stream), "mindiesd_copy_2d")

@@ -12,6 +12,7 @@ import torch
 from .attention_func import attention_math
 from .common import AttentionParam
 from ...utils.exception import ParametersInvalid
+from ...utils.status import checked
 
 _SUPPORTED_FA_TYPES = {"prompt_flash_attn", "fused_attn_score", "ascend_laser_attention"}
 _SUPPORTED_LAYOUTS = {"BNSD", "BSND", "BSH"}
@@ -46,7 +47,7 @@ def attention_forward(query, key, value, attn_mask=None, scale=None, fused=True,
                                 "use fused=False for a masked evaluation.")
     if query.dtype not in (torch.bfloat16, torch.float16):
         raise ParametersInvalid(f"The fused attention kernel supports bfloat16 and float16, but got {query.dtype}.")
-    return torch.ops.mindiesd.attention_fwd(query, key, value, float(scale), bool(head_first))
+    return checked(torch.ops.mindiesd.attention_fwd(query, key, value, float(scale), bool(head_first)), "attention_forward")
 
 
 def check_input_params(input_params):

@@ -15,6 +15,7 @@ from typing import Optional
 import torch
 
 from ...utils.exception import ParametersInvalid
+from ...utils.status import checked
 
 
 @dataclass
@@ -69,7 +70,8 @@ def attention_forward_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: 
         # Host-side lengths can be checked without touching the device.
         if int(cu_seqlens_q[-1]) != q.shape[0] or int(cu_seqlens_k[-1]) != k.shape[0]:
             raise ParametersInvalid("cu_seqlens_q / cu_seqlens_k must hold batch + 1 cumulative lengths ending at T.")
-    return torch.ops.mindiesd.attention_varlen_fwd(q, k, v, cu_q, cu_k, float(softmax_scale), bool(causal))
+    return checked(torch.ops.mindiesd.attention_varlen_fwd(q, k, v, cu_q, cu_k, float(softmax_scale), bool(causal)),
+                   "attention_forward_varlen")
 
 
 def _as_device_int32(cu_seqlens, device):

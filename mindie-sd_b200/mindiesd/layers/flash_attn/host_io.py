@@ -14,6 +14,7 @@ from typing import Optional
 import torch
 
 from ...utils.exception import ParametersInvalid
+from ...utils.status import raise_if_kernel_gave_up
 
 
 _STAGING = {}  # device index -> (key, buffers, streams): one set of staging buffers per device, reused across calls
@@ -113,4 +114,5 @@ def _run_pipeline(query, key, value, out, scale, head_chunks, hc, device):
     # The calling stream is ordered after the last copy out, and so is the host.
     compute.wait_event(stored[head_chunks - 1])
     stored[head_chunks - 1].synchronize()
+    raise_if_kernel_gave_up("attention_forward_host")  # the call has synchronised anyway
     return out

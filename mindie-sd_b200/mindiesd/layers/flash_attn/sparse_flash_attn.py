@@ -8,6 +8,7 @@ from .sparse_flash_attn_ada_bsa import ada_block_sparse_attention, get_estimate_
 from .sparse_flash_attn_rf_v2 import rain_fusion_attention
 from .sparse_flash_attn_rf_v3 import bsa_sparse_attention_v3, do_tensor_rearrange_only
 from ...utils.exception import ParametersInvalid
+from ...utils.status import checked
 
 MAX_TOKEN = 2147483647
 
@@ -62,4 +63,4 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attn_mas
                                          input_layout=input_layout, sparse_size=block_size)
     else:
         out = torch.ops.mindiesd.attention_fwd(q, k, v, float(scale), input_layout == "BNSD")
-    return out
+    return checked(out, "sparse_attention")

@@ -24,6 +24,7 @@ import torch
 import torch.distributed as dist
 
 from ..utils.exception import ParametersInvalid
+from ..utils.status import raise_if_kernel_gave_up
 
 _ROPE_MODES = {"rotated_half": 1, "rotated_interleaved": 2}
 
@@ -168,7 +169,9 @@ def _move(tensors, table, rows, world, n_loc, head0, heads, inverse=False, rope=
 
 def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, group=None,
                       scale: Optional[float] = None, head_chunks: Union[None, int, Sequence[int]] = None,
-                      attn_fn: Optional[Callable] = None, rope=None, profile: Optional[dict] = None) -> torch.Tensor:
+                      attn_fn: Optional[Callable] = None, rope=None, profile: Optional[dict] = None,
+                      _piece_ready: Optional[Callable] = None, _piece_done: Optional[Callable] = None,
+                      _out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """query/key/value: this rank's [B, S/P, N, D] slice (BSND).  Returns this rank's [B, S/P, N, D]
     slice of the attention output over the full sequence.
 
@@ -212,7 +215,7 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
     q, k, v = (x if x.is_contiguous() else x.contiguous() for x in (query, key, value))
     rows = b * s_loc
     qr, kr, vr = (x.view(rows, n, d) for x in (q, k, v))
-    out = torch.empty_like(q)
+    out = _out if _out is not None else torch.empty_like(q)
     outr = out.view(rows, n, d)
 
     # One set of buffers per piece: a piece's buffers are free again when the call returns.
@@ -243,6 +246,8 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
         """Pack piece c for every destination and start its all-to-all (communication stream)."""
         send, recv = bufs[4 * c], bufs[4 * c + 1]
         with on_comm():
+            if _piece_ready is not None:
+                _piece_ready(c, head0, sizes[c], comm)  # e.g. wait for the piece's heads to arrive from the host
             with timer.span("pack", comm):
                 _move((qr, kr, vr), send, rows, world, n_loc, head0, sizes[c], rope=rope_args,
                       thread_blocks=0 if c == 0 else 32)
@@ -282,6 +287,8 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
             compute.wait_event(ev)
         with timer.span("unpack", compute):
             _move((outr,), bufs[4 * c + 3], rows, world, n_loc, head0, sizes[c], inverse=True)
+        if _piece_done is not None:
+            _piece_done(c, head0, sizes[c], compute)  # e.g. start the piece's copy back to the host
 
     head0 = [sum(sizes[:c]) for c in range(len(sizes))]
     arrived = exchange_in(0, head0[0])
@@ -303,4 +310,76 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
         # orders itself behind this one on both streams.
         comm.wait_stream(compute)
     timer.finish()
+    return out
+
+
+_HOST_STAGING = {}
+
+
+def ulysses_attention_host(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, out: Optional[torch.Tensor] = None,
+                           group=None, scale: Optional[float] = None,
+                           head_chunks: Union[None, int, Sequence[int]] = None, device=None) -> torch.Tensor:
+    """`ulysses_attention` on operands that live in pinned host memory: this rank's [B, S/P, N, D] slices in,
+    a pinned [B, S/P, N, D] slice out.  The copies are pipelined with the exchange and the attention piece
+    by piece: the heads of piece c+1 cross PCIe (strided copies, one per tensor) while piece c is exchanged
+    and computed, and piece c-1's output columns go back to the host behind them, so only the first piece's
+    copy in and the last piece's copy out are exposed.  Returns after the last copy has landed."""
+    from .. import _cabi
+    for name, x in (("query", query), ("key", key), ("value", value)):
+        if not isinstance(x, torch.Tensor) or x.dim() != 4 or x.is_cuda or not x.is_pinned() or not x.is_contiguous():
+            raise ParametersInvalid(f"The input {name} must be a contiguous 4-D tensor in pinned host memory.")
+    if key.shape != query.shape or value.shape != query.shape or key.dtype != query.dtype or value.dtype != query.dtype:
+        raise ParametersInvalid("query, key and value must share shape and dtype.")
+    device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    world = dist.get_world_size(group)
+    b, s_loc, n, d = query.shape
+    if n % world:
+        raise ParametersInvalid(f"The head number {n} must be divisible by the sequence-parallel size {world}.")
+    if out is None:
+        out = torch.empty(query.shape, dtype=query.dtype, pin_memory=True)
+    n_loc = n // world
+    sizes = _piece_sizes(head_chunks, n_loc, s_loc * world, b)
+    skey = (device.index, tuple(query.shape), query.dtype)
+    if skey not in _HOST_STAGING:
+        _HOST_STAGING.clear()
+        _HOST_STAGING[skey] = ([torch.empty(query.shape, dtype=query.dtype, device=device) for _ in range(4)],
+                               torch.cuda.Stream(device), torch.cuda.Stream(device))
+    (dq, dk, dv, do), copy_in, copy_out = _HOST_STAGING[skey]
+    compute = torch.cuda.current_stream(device)
+    copy_in.wait_stream(compute)
+    copy_out.wait_stream(compute)
+    esz = query.element_size()
+    pitch = n_loc * d * esz          # one destination rank's head group of one token
+    height = b * s_loc * world       # (token, destination rank) pairs
+
+    def start_copy_in(head0, heads):
+        off = head0 * d * esz
+        for dst, src in ((dq, query), (dk, key), (dv, value)):
+            _cabi.copy_2d(dst.data_ptr() + off, pitch, src.data_ptr() + off, pitch, heads * d * esz, height, copy_in)
+        ev = torch.cuda.Event()
+        ev.record(copy_in)
+        return ev
+
+    head0 = [sum(sizes[:c]) for c in range(len(sizes))]
+    arrived = [start_copy_in(head0[c], sizes[c]) for c in range(len(sizes))]  # the copy engine takes them in order
+    copied_out = []
+
+    def piece_ready(c, h0, heads, stream):
+        stream.wait_event(arrived[c])
+
+    def piece_done(c, h0, heads, stream):
+        ev = torch.cuda.Event()
+        ev.record(stream)
+        copy_out.wait_event(ev)
+        off = h0 * d * esz
+        _cabi.copy_2d(out.data_ptr() + off, pitch, do.data_ptr() + off, pitch, heads * d * esz, height, copy_out)
+        done = torch.cuda.Event()
+        done.record(copy_out)
+        copied_out.append(done)
+
+    ulysses_attention(dq, dk, dv, group=group, scale=scale, head_chunks=sizes, _piece_ready=piece_ready,
+                      _piece_done=piece_done, _out=do)
+    compute.wait_event(copied_out[-1])
+    copied_out[-1].synchronize()
+    raise_if_kernel_gave_up("ulysses_attention_host")  # the call has synchronised anyway
     return out

@@ -7,6 +7,7 @@ from torch import nn
 
 from ..layers.quant.block_quant import fa_block_quant_preprocess, fa_channel_quant_preprocess
 from ..utils.exception import ParametersInvalid
+from ..utils.status import checked
 
 
 def get_quant_weight(weights, name):
@@ -53,7 +54,7 @@ class FP8RotateQuantFA(nn.Module):
             v_block = 256
         out = torch.ops.mindiesd.fp8_attention(q, k, v, q_scale, k_scale, v_scale, 1.0 / math.sqrt(d), 256, v_block,
                                                query.dtype)
-        return out.transpose(1, 2) if layout == "BSND" else out
+        return checked(out.transpose(1, 2) if layout == "BSND" else out, "FP8RotateQuantFA")
 
 
 def add_fa_quant(module, prefix=None, weights=None):

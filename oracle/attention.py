@@ -61,12 +61,13 @@ def attention_math_chunked(query, key, value, scale=None, head_first=False, rows
     return out
 
 
-def block_sparse_attention(query, key, value, block_mask, block=128, scale=None):
+def block_sparse_attention(query, key, value, block_mask, block=128, scale=None, q_blocks=None):
     """Restates `block_sparse_attention_cpu`, tests/plugin/test_block_sparse_attention.py:32-65.
 
     BNSD inputs; block_mask int8 [B, N, q_blocks, kv_blocks], 1 = attend.  Each q block attends to
     the keys of its kept blocks only; fp32 arithmetic; a row that keeps nothing yields zeros.
-    Returns fp32 [B, N, S, D].
+    Returns fp32 [B, N, S, D].  `q_blocks` restricts the evaluation to those query blocks (the other
+    rows of the result stay zero): the same arithmetic per block at a bounded cost.
     """
     b, nq, s, d = query.shape
     nkv = key.shape[1]
@@ -83,7 +84,7 @@ def block_sparse_attention(query, key, value, block_mask, block=128, scale=None)
     kblocks = math.ceil(skv / block)
     for bi in range(b):
         for ni in range(nq):
-            for qb in range(qblocks):
+            for qb in (range(qblocks) if q_blocks is None else q_blocks):
                 keep = np.repeat(m[bi, ni, qb, :kblocks], block)[:skv].astype(bool)
                 r0, r1 = qb * block, min((qb + 1) * block, s)
                 if not keep.any():

@@ -85,3 +85,17 @@ def test_block_sparse_lse_with_actual_length_below_padded_length():
     want_out = oa.attention_math(q[:, :, :real].cpu(), k[:, :, :real].cpu(), v[:, :, :real].cpu(), head_first=True)
     assert (out[:, :, :real].float().cpu() - want_out.float()).abs().max().item() <= 2e-2
     assert torch.count_nonzero(out[:, :, real:]).item() == 0
+
+
+def test_layer_api_raises_when_asked_to_check(monkeypatch):
+    """MINDIESD_CHECK_STATUS=1: the layer entry reads the status word after its call and raises."""
+    from mindiesd import _cabi, attention_forward, ModelExecError
+    assert _cabi.device_status() == 0
+    q, k, v = (inputs.randn(830 + i, 1, 300, 2, 128, dtype=torch.bfloat16).cuda() for i in range(3))
+    _cabi.attention(q, k, v, head_first=False, wait_limit_us=20000, test_withhold=1)  # sets the word
+    monkeypatch.setenv("MINDIESD_CHECK_STATUS", "1")
+    with pytest.raises(ModelExecError):
+        attention_forward(q, k, v)
+    out = attention_forward(q, k, v)  # the word was cleared by the check: back to normal
+    want = oa.attention_math(q.cpu(), k.cpu(), v.cpu(), head_first=False)
+    assert (out.float().cpu() - want.float()).abs().max().item() <= 2e-2

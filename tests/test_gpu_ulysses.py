@@ -29,22 +29,41 @@ def _worker(rank, world, port, head_chunks, result):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         import inputs
-        from mindiesd import _cabi, ulysses_attention
+        from mindiesd import _cabi, rotary_position_embedding, ulysses_attention
+        from mindiesd.parallel import ulysses_attention_host
         n, s = 8, 3000 if world == 2 else 4096  # 3000 / 2 = 1500 rows per rank: ragged 128-row tiles
         q, k, v = (inputs.randn(400 + i, 1, s, n, 128, dtype=torch.bfloat16).cuda() for i in range(3))
         want = _cabi.attention(q, k, v, head_first=False)
         shard = lambda x: x.chunk(world, dim=1)[rank].contiguous()  # noqa: E731
-        out = ulysses_attention(shard(q), shard(k), shard(v), head_chunks=head_chunks)
-        torch.cuda.synchronize()
-        # the same kernel on the same rows and heads: only the walk order of the heads differs
-        ok = torch.equal(out, shard(want))
-        ok = ok and _cabi.device_status() == 0
-        result[rank] = bool(ok)
+        checks = {}
+        for rep in range(2):  # the second call reuses the persistent buffers
+            out = ulysses_attention(shard(q), shard(k), shard(v), head_chunks=head_chunks)
+            torch.cuda.synchronize()
+            # the same kernel on the same rows and heads: only the walk order of the heads differs
+            checks[f"plain{rep}"] = torch.equal(out, shard(want))
+        # rotary embedding inside the exchange == rotary_position_embedding, then attention, on one GPU
+        cos, sin = (inputs.randn(410 + i, s, 128).cuda() for i in range(2))
+        for mode in ("rotated_half", "rotated_interleaved"):
+            qr, kr = (rotary_position_embedding(x, cos, sin, mode, head_first=False) for x in (q, k))
+            want_r = _cabi.attention(qr, kr, v, head_first=False)
+            cs, ss = (x.chunk(world, dim=0)[rank].contiguous() for x in (cos, sin))
+            out_r = ulysses_attention(shard(q), shard(k), shard(v), head_chunks=head_chunks, rope=(cs, ss, mode))
+            checks[mode] = torch.equal(out_r, shard(want_r))
+        # operands in pinned host memory, copies pipelined with the pieces
+        hq, hk, hv = (shard(x).cpu().pin_memory() for x in (q, k, v))
+        for rep in range(2):
+            ho = ulysses_attention_host(hq, hk, hv, head_chunks=head_chunks)
+            checks[f"host{rep}"] = torch.equal(ho, shard(want).cpu())
+        prof = {}
+        ulysses_attention(shard(q), shard(k), shard(v), head_chunks=head_chunks, profile=prof)
+        checks["profile"] = set(prof) == {"pack", "exchange_in", "attention", "exchange_out", "unpack"}
+        checks["status"] = _cabi.device_status() == 0
+        result[rank] = {k_: bool(v_) for k_, v_ in checks.items()}
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,head_chunks", [(2, 1), (2, 4), (4, 2)])
+@pytest.mark.parametrize("world,head_chunks", [(2, 1), (2, 4), (2, (1, 3)), (4, 2)])
 def test_ulysses_equals_single_gpu(world, head_chunks):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
@@ -57,4 +76,34 @@ def test_ulysses_equals_single_gpu(world, head_chunks):
     for p in procs:
         p.join(timeout=300)
         assert p.exitcode == 0
-    assert all(result.get(r) for r in range(world)), dict(result)
+    for r in range(world):
+        assert result.get(r) and all(result[r].values()), dict(result)
+
+
+def test_reshard_kernel_on_one_gpu():
+    """mindiesd_ulysses_move by itself (one GPU plays every rank): forward into a send buffer, with and without
+    the rotary embedding, against torch indexing and the rotary oracle; the inverse restores the layout."""
+    import inputs
+    from oracle import rope as orope
+    from mindiesd import _cabi
+    world, rows, n, d = 4, 333, 8, 128
+    n_loc, head0, h = n // world, 1, 1
+    q, k, v = (inputs.randn(420 + i, rows, n, d, dtype=torch.bfloat16) for i in range(3))
+    cos, sin = (inputs.randn(430 + i, rows, d) for i in range(2))
+    for mode_name, mode in ((None, 0), ("rotated_half", 1), ("rotated_interleaved", 2)):
+        send = torch.zeros(world, rows, 3 * h, d, dtype=torch.bfloat16, device="cuda")
+        _cabi.ulysses_move((q.cuda(), k.cuda(), v.cuda()), [send[r].data_ptr() for r in range(world)], send.stride(1), rows,
+                           world, n_loc, head0, h, cos=cos.cuda(), sin=sin.cuda(), rope_mode=mode, thread_blocks=7)
+        for i, x in enumerate((q, k, v)):
+            if mode and i < 2:
+                x = orope.rotary_position_embedding(x[None], cos, sin, mode_name, head_first=False)[0]
+            want = x.view(rows, world, n_loc, d)[:, :, head0:head0 + h].permute(1, 0, 2, 3)
+            assert torch.equal(send[:, :, i * h:(i + 1) * h].cpu(), want), (mode_name, i)
+    o_recv = inputs.randn(440, world, rows, h, d, dtype=torch.bfloat16).cuda()
+    out = torch.zeros(rows, n, d, dtype=torch.bfloat16, device="cuda")
+    _cabi.ulysses_move((out,), [o_recv[r].data_ptr() for r in range(world)], o_recv.stride(1), rows, world, n_loc, head0, h,
+                       inverse=True)
+    want = torch.zeros(rows, world, n_loc, d, dtype=torch.bfloat16)
+    want[:, :, head0:head0 + h] = o_recv.cpu().permute(1, 0, 2, 3)
+    assert torch.equal(out.cpu().view(rows, world, n_loc, d), want)
+    assert _cabi.device_status() == 0
