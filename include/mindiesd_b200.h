@@ -322,7 +322,11 @@ int mindiesd_fa_rotate_quant(const mindiesd_rotate_quant_args* args, void* strea
  *   scratch: at least mindiesd_sparse_block_estimate_scratch_bytes(1, 1, seq) bytes (one head per
  *           pass); the size that function returns for the real batch and heads lets four heads
  *           run per pass, whose partial sums stay in L2
- * causal != 0 is not supported (MINDIESD_E_VALUE).
+ * causal != 0 follows the golden's causal branch (:73-76, 129-143): the queries of a 1024-token chunk take
+ * their softmax over the keys up to the end of that chunk, a query block ranks the key blocks up to its
+ * own with its own block's mass cleared (it is kept only if the guard is 0), rows 0 and 1 keep every
+ * block up to their own, the first block always stays, the cap is int(row_sparse * (row + 1)), and
+ * blocks beyond the row's own are 0.  keep_recent has no effect then.
  *
  * Stands in for: aclnnSparseBlockEstimate as registered in csrc/plugin/register_ops.cpp:46-53 and
  * called by mindiesd/layers/flash_attn/sparse_flash_attn_ada_bsa.py:31-47; semantics pinned by
@@ -340,13 +344,16 @@ typedef struct mindiesd_estimate_args {
     float scale;         /* multiplies the pooled dot product; the layer passes softmax_scale / stride */
     float threshold;     /* share of a row's mass the kept prefix must reach */
     double row_sparse;   /* cap on the kept prefix as a share of the row; <= 0 or >= 1: no cap */
-    int32_t causal;      /* must be 0 */
+    int32_t causal;
     int32_t keep_sink, keep_recent;
     int8_t* mask;
     int32_t mask_cols;
     int32_t* count;
     void* scratch;
     size_t scratch_bytes;
+    /* causal only: key tokens that exist when `seq` was rounded up to a multiple of 8 with zero tokens --
+       the golden drops a trailing partial group of keys in its causal branch (:73-76); 0 = seq. */
+    int32_t causal_key_tokens;
 } mindiesd_estimate_args;
 
 size_t mindiesd_sparse_block_estimate_scratch_bytes(int32_t batch, int32_t heads, int32_t seq);

@@ -33,22 +33,35 @@ constexpr int kMmaWarp = 8;
 constexpr int kLoadWarp = 9;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
-// Register budgets after the roles split: 2 x 128 x kRegsSoftmax + 128 x kRegsOther <= 65536.
+// Register budgets after the roles split.  The registers a warpgroup may take are the ones another
+// warpgroup of the SAME thread block gave back: the pool is what the launch gave the block (threads x
+// registers per thread as compiled, 384 x 168), not the SM's register file.  A request beyond it never
+// returns -- there is no time limit on that wait -- so the sum is checked here.
 #ifndef SDB_FA_REGS_SOFTMAX
-#define SDB_FA_REGS_SOFTMAX 224
+#define SDB_FA_REGS_SOFTMAX 216
 #endif
 #ifndef SDB_FA_REGS_OTHER
-#define SDB_FA_REGS_OTHER 64
+#define SDB_FA_REGS_OTHER 72
 #endif
-// Two-byte operands: hand the probabilities of a block to the MMA thread in two halves (keys 0-63, 64-127),
-// so that the first half of the P V product runs under the second half of the exponentials.
-#ifndef SDB_FA_HALVES
-#define SDB_FA_HALVES 0
+constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) compiles to: 65536 / 384 rounded down to 8
+// How the softmax warps treat a block of two-byte operands (e4m3 always uses the last form):
+//   0  exponentials against the running max right away, overflow caught by a row-sum test, P handed over whole
+//   1  the same in two halves of 64 keys
+//   2  block max first; P stored chunk by chunk as it is computed and handed over after 96 and 128
+//      keys; the row sum is taken after the hand-over, off the path the MMA thread waits on
+#ifndef SDB_FA_RESPLIT_FP8
+#define SDB_FA_RESPLIT_FP8 0
 #endif
-constexpr bool kHalves = SDB_FA_HALVES != 0;
+#ifndef SDB_FA_BF16_MODE
+#define SDB_FA_BF16_MODE 0
+#endif
+constexpr int kBf16Mode = SDB_FA_BF16_MODE;
+constexpr bool kHalves = kBf16Mode == 1;
+constexpr bool kMaxFirst = kBf16Mode == 2;
 constexpr int kRegsSoftmax = SDB_FA_REGS_SOFTMAX;
 constexpr int kRegsOther = SDB_FA_REGS_OTHER;
-static_assert(2 * 128 * kRegsSoftmax + 128 * kRegsOther <= 65536, "register file of one SM");
+static_assert(2 * 128 * kRegsSoftmax + 128 * kRegsOther <= 384 * kLaunchRegs, "register pool of one thread block");
+static_assert(kRegsSoftmax % 8 == 0 && kRegsOther % 8 == 0 && kRegsOther >= 24 && kRegsSoftmax <= 256, "setmaxnreg operand");
 constexpr float kRescaleThreshold = 8.0f;  // log2 units the running max may lag before O is rescaled
 constexpr float kFp8PShiftLog2 = 8.0f;     // e4m3 probabilities are stored as p * 2^8
 constexpr float kFp8Lag = 0.75f;           // 2^8.75 = 431 still fits e4m3 (max 448)
@@ -119,7 +132,11 @@ __device__ __forceinline__ void poison_row(const FaParams& p, int batch, int hea
 template <int kIn>
 __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_constant__ FaParams p) {
     constexpr bool kFp8 = kIn == 3;
-    constexpr bool kSplit = kFp8 || kHalves;  // P is handed to the MMA thread in two halves
+    constexpr bool kResplit = SDB_FA_RESPLIT_FP8 || !kFp8;  // whether the warpgroups re-split their registers
+    constexpr bool kSplit = kFp8 || kHalves || kMaxFirst;  // P is handed to the MMA thread in two parts
+    // 32-key chunks of a block in the first part: half of the block, or three quarters when the
+    // exponentials of a two-byte block are taken max-first (the second part's product is then short).
+    constexpr int kFirstChunks = (!kFp8 && kMaxFirst) ? 3 : 2;
     using C = Cfg<kFp8>;
     extern __shared__ uint8_t smem_raw[];
     // The swizzle pattern of TMA and of the MMA descriptors is a function of the address bits, so
@@ -282,7 +299,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     // The launch gives every thread 168: the last warpgroup hands most of its registers back and
     // each softmax warpgroup takes its share.
     if (warp >= 8) {
-      warpgroup_reg_dec<kRegsOther>();
+      if constexpr (kResplit) warpgroup_reg_dec<kRegsOther>();
       if (warp == kLoadWarp) {
         // ---- TMA producer ---------------------------------------------------------------------
         if (lane == 0) {
@@ -347,11 +364,12 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 }
                 umma_commit(bar_s(t));
             };
-            auto issue_pv = [&](int t, int h, int slot, bool accumulate) {  // keys 64h .. 64h+63 of the block
+            constexpr int kFirstSteps = C::kPvSteps * kFirstChunks / 4;
+            auto issue_pv = [&](int t, int h, int slot, bool accumulate) {  // first (h = 0) or second part of the block's keys
                 const uint32_t v_lo = ring_v_lo + slot * kSlotStep;
 #pragma unroll
-                for (int kk = 0; kk < C::kPvSteps / 2; ++kk) {
-                    const int kc = h * (C::kPvSteps / 2) + kk;
+                for (int kc = 0; kc < C::kPvSteps; ++kc) {
+                    if ((kc < kFirstSteps) != (h == 0)) continue;
                     umma_ts_lohi<kFp8>(col_o[t], col_s[t] + kc * 8, v_lo + kc * (C::kPvK * 128 >> 4), kDescHiSbo1024, idesc_pv,
                                        (accumulate || kc > 0) ? 1u : 0u);
                 }
@@ -389,7 +407,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                         if (!ok) break;
                         tc_fence_after();
                         issue_pv(0, 0, vslot.idx, pv_cnt[0] > 0);
-                        if constexpr (!kFp8) umma_commit(bar_h(0));
+                        if constexpr (kHalves && !kFp8) umma_commit(bar_h(0));
                     }
                     ok = mbar_wait(bar_p(0, 1), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13, wait_us);
                     if (!ok) break;
@@ -410,7 +428,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                         if (!ok) break;
                         tc_fence_after();
                         issue_pv(1, 0, vslot.idx, pv_cnt[1] > 0);
-                        if constexpr (!kFp8) umma_commit(bar_h(1));
+                        if constexpr (kHalves && !kFp8) umma_commit(bar_h(1));
                     }
                     ok = mbar_wait(bar_p(1, 1), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14, wait_us);
                     if (!ok) break;
@@ -435,7 +453,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         }
       }
     } else {
-        warpgroup_reg_inc<kRegsSoftmax>();
+        if constexpr (kResplit) warpgroup_reg_inc<kRegsSoftmax>();
         // ---- softmax, O rescale, epilogue: one query row per thread ------------------------------
         const int t = warp >> 2;  // tile of this warpgroup
         const int row_in_tile = tid & (kTile - 1);
@@ -622,7 +640,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 ok = half(std::integral_constant<int, 0>{});
                 if (ok) ok = half(std::integral_constant<int, 1>{});
                 if (!ok) break;
-            } else if constexpr (!kFp8) {
+            } else if constexpr (!kFp8 && !kMaxFirst) {
                 // The probabilities are taken against the running max right away and kept in registers; the
                 // scores die as they are consumed.  Every probability is non-negative, so a row sum within
                 // 2^lag bounds each of them: only if that test fails somewhere in the warp -- rare after the
@@ -721,7 +739,6 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 // x = s * mult - m as packed pairs (one instruction per two scores), then ex2 and pack.
                 const float neg_m = m_run == -INFINITY ? 0.0f : (kFp8 ? (kFp8PShiftLog2 + v_off - m_run) : -m_run);
                 const uint64_t mult2 = pack2(mult, mult), negm2 = pack2(neg_m, neg_m);
-                uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
     #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t pk[kFp8 ? 8 : 16];
@@ -734,8 +751,11 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                         unpack2(fma2(pack2(__uint_as_float(s[c][4 * i + 2]), __uint_as_float(s[c][4 * i + 3])), mult2, negm2), e2, e3);
                         e2 = ex2_approx(e2);
                         e3 = ex2_approx(e3);
-                        sum2[0] = add2(sum2[0], pack2(e0, e1));
-                        sum2[1] = add2(sum2[1], pack2(e2, e3));
+                        // kept in place of the scores: the row sum is taken after the hand-over
+                        s[c][4 * i] = __float_as_uint(e0);
+                        s[c][4 * i + 1] = __float_as_uint(e1);
+                        s[c][4 * i + 2] = __float_as_uint(e2);
+                        s[c][4 * i + 3] = __float_as_uint(e3);
                         if constexpr (kFp8) {
                             pk[i] = pack_quad_e4m3(e0, e1, e2, e3);
                         } else {
@@ -743,17 +763,25 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                             pk[2 * i + 1] = pack_pair(e2, e3, kIn);
                         }
                     }
+                    // The packed chunk lands on columns whose scores are already in registers.
                     if constexpr (kFp8) tmem_st8(taddr_s + c * 8, pk);
                     else tmem_st16(taddr_s + c * 16, pk);
-                    if (c & 1) {  // a half of the block's keys is complete: hand it over
+                    if (c == kFirstChunks - 1 || c == 3) {  // a part of the block's keys is complete: hand it over
                         tmem_wait_st();
                         tc_fence_before();
-                        mbar_arrive(bar_p(t, c >> 1));
+                        mbar_arrive(bar_p(t, c == 3 ? 1 : 0));
                     }
                 }
+                // The row sum, while the MMA thread is busy with what it was just handed.
                 {
+                    uint64_t sum2[4] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f), pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
+    #pragma unroll
+                    for (int c = 0; c < 4; ++c)
+    #pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            sum2[i & 3] = add2(sum2[i & 3], pack2(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])));
                     float a, b;
-                    unpack2(add2(sum2[0], sum2[1]), a, b);
+                    unpack2(add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3])), a, b);
                     l_run += (a + b) * l_fix;
                 }
             }
@@ -843,6 +871,14 @@ static cudaError_t launch_one(const FaParams& p, cudaStream_t stream) {
     const int smem = fa_fwd_smem_bytes(kIn == 3);
     cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<kIn>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
+    // The kernel's warpgroups re-split the registers the launch gives the block; if this build of the
+    // kernel was given fewer than the split assumes, the request would wait forever.  Refuse instead.
+    static const int launch_regs = [] {
+        cudaFuncAttributes attr;
+        return cudaFuncGetAttributes(&attr, fa_fwd_kernel<kIn>) == cudaSuccess ? attr.numRegs : 0;
+    }();
+    if ((SDB_FA_RESPLIT_FP8 || kIn != 3) && 2 * 128 * kRegsSoftmax + 128 * kRegsOther > kThreads * launch_regs)
+        return cudaErrorLaunchOutOfResources;
     // Packed sequences: every sequence rounds its tile pairs up, so seq_q / 256 + num_seqs bounds their number.
     const int pairs = p.cu_seqlens_q ? p.seq_q / (2 * kTile) + p.num_seqs : (p.seq_q + 2 * kTile - 1) / (2 * kTile);
     dim3 grid(pairs, p.heads, p.batch);

@@ -57,6 +57,10 @@ struct SbeParams {
     int slices;           // K slices per trip: 8 tokens x head_dim / 64
     int slices_per_token; // head_dim / 64
     float scale_log2;
+    // Causal form of the reference's golden: the 128 query groups of a thread block (1024 tokens) see the
+    // key groups up to the end of their own 1024-token chunk -- the softmax runs over those -- and each
+    // query block then ranks the key blocks up to its own.  key_groups: key groups that exist.
+    int causal, key_groups;
     int* status;
 };
 
@@ -105,6 +109,9 @@ __global__ void __launch_bounds__(kThreads1, 1) sbe_partial_kernel(const __grid_
     // once per thread block (all of its threads stay or all leave: the ones that stay set up barriers
     // and tensor memory for the others).
     if (__syncthreads_or(tid == 0 && p.status && *reinterpret_cast<volatile int*>(p.status) != 0)) return;
+    // Key groups this thread block's rows take their softmax over, and the trips that cover them.
+    const int my_groups = p.causal ? min(p.key_groups, g0 + kRows) : p.groups;
+    const int my_trips = (my_groups + kCols - 1) / kCols;
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -138,7 +145,7 @@ __global__ void __launch_bounds__(kThreads1, 1) sbe_partial_kernel(const __grid_
             Ring ring;
             int issued = 0;
             bool ok = true;
-            for (int trip = 0; trip < p.trips && ok; ++trip) {
+            for (int trip = 0; trip < my_trips && ok; ++trip) {
                 for (int c = 0; c < p.slices && ok; ++c) {
                     ok = mbar_wait(bar_empty(ring.idx), ring.phase ^ 1u, abort_flag, 1);
                     if (!ok) break;
@@ -166,7 +173,7 @@ __global__ void __launch_bounds__(kThreads1, 1) sbe_partial_kernel(const __grid_
             constexpr uint32_t kStageStep = kStageBytes >> 4;
             Ring ring;
             bool ok = true;
-            for (int trip = 0; trip < p.trips && ok; ++trip) {
+            for (int trip = 0; trip < my_trips && ok; ++trip) {
                 const int buf = trip & 1;
                 ok = mbar_wait(bar_acc_empty(buf), (static_cast<uint32_t>(trip >> 1) & 1u) ^ 1u, abort_flag, 10);
                 if (!ok) break;
@@ -194,13 +201,13 @@ __global__ void __launch_bounds__(kThreads1, 1) sbe_partial_kernel(const __grid_
         float* mrow = p.used_max + (static_cast<int64_t>(blockIdx.y) * p.groups_pad + g) * p.trips;
         float m_run = -INFINITY;  // running maximum of the raw accumulators
         bool ok = true;
-        for (int trip = 0; trip < p.trips && ok; ++trip) {
+        for (int trip = 0; trip < my_trips && ok; ++trip) {
             const int buf = trip & 1;
             ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full(buf), static_cast<uint32_t>(trip >> 1) & 1u, abort_flag, 20));
             if (!ok) break;
             tc_fence_after();
             const uint32_t t0 = tmem_base + lane_base + buf * kCols;
-            const int valid = min(kCols, p.groups - trip * kCols);  // key groups of this trip that exist
+            const int valid = min(kCols, my_groups - trip * kCols);  // key groups of this trip that exist (and are seen)
             // Pass 1: the trip's maximum.  The accumulator is read twice rather than held in 256 registers.
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             for (int c0 = 0; c0 < valid; c0 += 32) {
@@ -292,6 +299,8 @@ struct SelectParams {
     float threshold;
     int max_keep;   // cap on the kept prefix (row_sparse), or blocks
     int keep_sink, keep_recent;
+    int causal, key_groups;
+    double row_sparse;  // causal: the cap is int(row_sparse * (blocks up to the row's own)), per row
     int8_t* mask;   // [batch][heads][blocks][mask_cols]
     int32_t* count; // [batch][heads][blocks]
 };
@@ -313,13 +322,19 @@ __global__ void __launch_bounds__(kThreads2) sbe_select_kernel(const SelectParam
     const int cols = p.trips * kTripBlocks;  // pitch of a partial row
     const int64_t row_base = static_cast<int64_t>(blockIdx.y) * p.groups_pad + static_cast<int64_t>(qb) * kBlockGroups;
     const int nrows = min(kBlockGroups, p.groups - qb * kBlockGroups);
+    // Causal: the row's softmax ran over the key groups up to the end of its 1024-token chunk (what kernel 1
+    // wrote); the blocks that compete are those up to the row's own.
+    const int seen_groups = p.causal ? min(p.key_groups, (qb / (kRows / kBlockGroups) + 1) * kRows) : p.groups;
+    const int trips_q = p.causal ? (seen_groups + kCols - 1) / kCols : p.trips;
+    const int seen_blocks = p.causal ? (seen_groups + kBlockGroups - 1) / kBlockGroups : p.blocks;
+    const int nb = p.causal ? min(qb + 1, seen_blocks) : p.blocks;  // blocks that compete
 
     for (int i = tid; i < kBlockGroups * p.trips; i += kThreads2) {
         const int r = i / p.trips, t = i - r * p.trips;
         float f = 0.f;
-        if (r < nrows) {
+        if (r < nrows && t < trips_q) {
             const float* m = p.used_max + (row_base + r) * p.trips;
-            f = ex2_approx(m[t] - m[p.trips - 1]);
+            f = ex2_approx(m[t] - m[trips_q - 1]);
         }
         factor[r][t] = f;
     }
@@ -330,7 +345,7 @@ __global__ void __launch_bounds__(kThreads2) sbe_select_kernel(const SelectParam
         float s = 0.f;
         if (r < nrows) {
             const float* pr = p.partial + (row_base + r) * cols;
-            for (int j = lane; j < p.blocks; j += 32) s += pr[j] * factor[r][j / kTripBlocks];
+            for (int j = lane; j < seen_blocks; j += 32) s += pr[j] * factor[r][j / kTripBlocks];
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
@@ -342,12 +357,19 @@ __global__ void __launch_bounds__(kThreads2) sbe_select_kernel(const SelectParam
         if (r < nrows) factor[r][t] = factor[r][t] / row_sum[r];
     }
     __syncthreads();
-    for (int j = tid; j < p.blocks; j += kThreads2) {
+    for (int j = tid; j < nb; j += kThreads2) {
         const int t = j / kTripBlocks;
         float s = 0.f;
         for (int r = 0; r < nrows; ++r) s += p.partial[(row_base + r) * cols + j] * factor[r][t];
-        if (p.keep_recent && j == p.blocks - 1) s = 0.f;  // the last block is kept anyway and does not compete
+        // The last block does not compete: kept anyway (keep_recent), or -- causal -- the row's own block,
+        // whose mass the golden clears before ranking.
+        if ((p.keep_recent || p.causal) && j == nb - 1) s = 0.f;
         score[j] = s;
+    }
+    int max_keep = p.max_keep;
+    if (p.causal) {
+        max_keep = nb;
+        if (p.row_sparse > 0.0 && p.row_sparse * nb < nb) max_keep = max(1, static_cast<int>(p.row_sparse * nb));
     }
     __syncthreads();
     // The guard is the score of the block at which the running sum of the descending scores first reaches
@@ -361,14 +383,15 @@ __global__ void __launch_bounds__(kThreads2) sbe_select_kernel(const SelectParam
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i) {
             const int j = lane + 32 * i;
-            x[i] = j < p.blocks ? score[j] : -1.f;  // padding never reaches a candidate
+            x[i] = j < nb ? score[j] : -1.f;  // padding never reaches a candidate
             total += fmaxf(x[i], 0.f);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
         const float limit = p.threshold * total;
         uint32_t thr = 0;
-        if (total > 0.f) {
+        // Causal rows 0 and 1 keep every block up to their own (guard 0).
+        if (total > 0.f && !(p.causal && qb <= 1)) {
             for (int bit = 30; bit >= 0; --bit) {
                 const uint32_t cand = thr | (1u << bit);
                 float mass = 0.f;
@@ -382,7 +405,7 @@ __global__ void __launch_bounds__(kThreads2) sbe_select_kernel(const SelectParam
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) mass += __shfl_xor_sync(0xffffffffu, mass, o);
                 cnt = __reduce_add_sync(0xffffffffu, cnt);
-                if (mass >= limit || cnt >= p.max_keep) thr = cand;
+                if (mass >= limit || cnt >= max_keep) thr = cand;
             }
         }
         if (lane == 0) guard_smem = thr;
@@ -393,8 +416,9 @@ __global__ void __launch_bounds__(kThreads2) sbe_select_kernel(const SelectParam
     int kept = 0;
     for (int j = tid; j < p.mask_cols; j += kThreads2) {
         bool keep = false;
-        if (j < p.blocks)
-            keep = __float_as_uint(score[j]) >= guard || (p.keep_sink && j == 0) || (p.keep_recent && j == p.blocks - 1);
+        if (j < nb)
+            keep = __float_as_uint(score[j]) >= guard || (p.keep_sink && j == 0) ||
+                   (!p.causal && p.keep_recent && j == p.blocks - 1);
         mrow[j] = keep ? 1 : 0;
         kept += keep;
     }
@@ -481,7 +505,7 @@ extern "C" int mindiesd_sparse_block_estimate(const mindiesd_estimate_args* a, v
     if (a->head_dim != 64 && a->head_dim != 128) return MINDIESD_E_SHAPE;
     if (a->stride != kGroup || a->sparse_size != 128) return MINDIESD_E_SHAPE;
     if (a->seq % kGroup) return MINDIESD_E_SHAPE;  // the caller pads the token axis with zeros
-    if (a->causal) return MINDIESD_E_VALUE;
+    if (a->causal && (a->causal_key_tokens < 0 || a->causal_key_tokens > a->seq)) return MINDIESD_E_VALUE;
     if (!(a->scale > 0.0f) || !(a->threshold >= 0.0f) || !(a->row_sparse >= 0.0)) return MINDIESD_E_VALUE;
     const Sizes s = sizes_of(a->seq);
     if (s.blocks > kMaxMaskBlocks) return MINDIESD_E_CAPACITY;
@@ -505,6 +529,8 @@ extern "C" int mindiesd_sparse_block_estimate(const mindiesd_estimate_args* a, v
     p.slices_per_token = a->head_dim / 64;
     p.slices = kGroup * p.slices_per_token;
     p.scale_log2 = a->scale * 1.4426950408889634f;
+    p.causal = a->causal != 0;
+    p.key_groups = (a->causal && a->causal_key_tokens > 0 ? a->causal_key_tokens : a->seq) / kGroup;
     p.status = device_status_word();
 
     SelectParams sp;
@@ -526,6 +552,9 @@ extern "C" int mindiesd_sparse_block_estimate(const mindiesd_estimate_args* a, v
     }
     sp.keep_sink = a->keep_sink ? 1 : 0;
     sp.keep_recent = a->keep_recent ? 1 : 0;
+    sp.causal = p.causal;
+    sp.key_groups = p.key_groups;
+    sp.row_sparse = a->row_sparse;
     sp.mask = a->mask;
     sp.count = a->count;
 

@@ -331,7 +331,6 @@ std::tuple<at::Tensor, at::Tensor> sparse_block_estimate_cuda(
     TORCH_CHECK(query.scalar_type() == key.scalar_type(), "sparse_block_estimate: query and key must share a dtype");
     TORCH_CHECK(!actual_seq_lengths.has_value() && !actual_seq_lengths_kv.has_value(),
                 "sparse_block_estimate: actual_seq_lengths are not supported");
-    TORCH_CHECK(!causal, "sparse_block_estimate: causal=True is not supported");
     TORCH_CHECK(stride == 8 && sparse_size == 128, "sparse_block_estimate: only stride=8 and sparse_size=128 are supported");
     bool head_first = true, head_first_k = true;
     at::Tensor q4 = view_4d(query, input_layout, num_heads, &head_first, "sparse_block_estimate");
@@ -367,9 +366,10 @@ std::tuple<at::Tensor, at::Tensor> sparse_block_estimate_cuda(
     a.scale = static_cast<float>(scale_value);
     a.threshold = static_cast<float>(threshold);
     a.row_sparse = row_sparse;
-    a.causal = 0;
     a.keep_sink = keep_sink;
     a.keep_recent = keep_recent;
+    a.causal = causal ? 1 : 0;
+    a.causal_key_tokens = static_cast<int32_t>(s);  // the length before the zero completion
     a.mask = mask.data_ptr<int8_t>();
     a.mask_cols = static_cast<int32_t>(cols);
     a.count = count.data_ptr<int32_t>();

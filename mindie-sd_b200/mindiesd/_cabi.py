@@ -128,6 +128,7 @@ class EstimateArgs(C.Structure):
         ("causal", C.c_int32), ("keep_sink", C.c_int32), ("keep_recent", C.c_int32),
         ("mask", C.c_void_p), ("mask_cols", C.c_int32), ("count", C.c_void_p),
         ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t),
+        ("causal_key_tokens", C.c_int32),
     ]
 
 
@@ -395,7 +396,7 @@ def rf_block_mask_static(q, k, grid, txt_len=0, sparsity=0.0, head_first=True, p
 
 
 def sparse_block_estimate(q, k, scale, threshold, row_sparse=1.0, head_first=True, keep_sink=True, keep_recent=True,
-                          scratch=None):
+                          scratch=None, causal=False, causal_key_tokens=0):
     """mindiesd_sparse_block_estimate on tensors whose token count is a multiple of 8.
     Returns (int8 mask [B, N, blocks, blocks rounded up to 32], int32 count [B, N, blocks])."""
     b, n, s, d = _dims(q, head_first)
@@ -415,7 +416,8 @@ def sparse_block_estimate(q, k, scale, threshold, row_sparse=1.0, head_first=Tru
     a.batch, a.heads, a.kv_heads, a.seq, a.head_dim = b, n, nkv, s, d
     a.stride, a.sparse_size = 8, 128
     a.scale, a.threshold, a.row_sparse = float(scale), float(threshold), float(row_sparse)
-    a.causal, a.keep_sink, a.keep_recent = 0, int(keep_sink), int(keep_recent)
+    a.causal, a.keep_sink, a.keep_recent = int(bool(causal)), int(keep_sink), int(keep_recent)
+    a.causal_key_tokens = int(causal_key_tokens)
     a.mask, a.mask_cols, a.count = mask.data_ptr(), cols, count.data_ptr()
     a.scratch, a.scratch_bytes = scratch.data_ptr(), scratch.numel()
     check(lib().mindiesd_sparse_block_estimate(C.byref(a), current_stream_ptr(q.device)),

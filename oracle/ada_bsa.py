@@ -3,7 +3,7 @@
 The reference implements the estimator and the attention as closed NPU kernels
 (csrc/ops/sparse_block_estimate, csrc/ops/ada_block_sparse_attention); what pins their results are
 the numpy goldens of its plugin tests, which this file restates:
-`sparse_estimate_cpu` (tests/plugin/test_sparseblockestimate.py:49-145, non-causal branch) and
+`sparse_estimate_cpu` (tests/plugin/test_sparseblockestimate.py:49-145, both branches) and
 `ada_block_sparse_attention_cpu` (tests/plugin/test_adablocksparseattention.py:35-87, identical to
 the block-sparse golden restated in oracle/attention.py when causal is off).
 
@@ -88,8 +88,71 @@ def select_blocks(scores, threshold, row_sparse=1.0, keep_sink=True, keep_recent
     return mask, mask.sum(-1).astype(np.int32)
 
 
+def block_scores_causal(q, k, scale_value, block=128, stride=8, rows_per_chunk=128):
+    """The causal branch of the golden (test_sparseblockestimate.py:62-124 with causal=True): the
+    queries are taken in chunks of rows_per_chunk * stride tokens (the golden's M = 128 query groups);
+    the groups of a chunk take their softmax over the key groups that end before the chunk's last token
+    (a trailing partial group of keys is dropped, :73-76) -- NOT token-level causality --, and the
+    probabilities are summed per block as in the other branch.  Returns (float64 [blocks, blocks] with
+    zeros beyond what a chunk sees, int [blocks]: how many key blocks each query block's chunk sees)."""
+    s, d = q.shape
+    reduce_size = block // stride
+    blocks = math.ceil(s / block)
+    out = np.zeros((blocks, blocks), dtype=np.float64)
+    seen = np.zeros(blocks, dtype=np.int64)
+    chunk_tokens = rows_per_chunk * stride
+    for c0 in range(0, s, chunk_tokens):
+        m = min(chunk_tokens, s - c0)
+        qc = q[c0:c0 + m]
+        if m % stride:
+            qc = np.concatenate([qc, np.zeros((stride - m % stride, d), dtype=np.float32)], 0)
+        groups_q = qc.shape[0] // stride
+        qg = qc.reshape(groups_q, stride, d)[:, ::-1, :].reshape(groups_q, stride * d)
+        kseq = (c0 + m) // stride * stride
+        kg = k[:kseq].reshape(kseq // stride, stride * d)
+        p = (qg.astype(np.float64) * scale_value) @ kg.T.astype(np.float64)
+        p = np.exp(p - p.max(-1, keepdims=True))
+        p = p / p.sum(-1, keepdims=True)
+        pad_c = (-p.shape[1]) % reduce_size
+        pad_r = (-p.shape[0]) % reduce_size
+        p = np.pad(p, ((0, pad_r), (0, pad_c)))
+        r = p.reshape(p.shape[0] // reduce_size, reduce_size, p.shape[1] // reduce_size, reduce_size).sum(axis=(1, 3))
+        qb0 = c0 // block
+        out[qb0:qb0 + r.shape[0], :r.shape[1]] = r[:blocks - qb0]
+        seen[qb0:qb0 + r.shape[0]] = r.shape[1]
+    return out, seen
+
+
+def select_blocks_causal(scores, seen, threshold, row_sparse=1.0, golden_rounding=False):
+    """The per-row decision of the golden's causal branch (test_sparseblockestimate.py:127-143): rows 0
+    and 1 keep every block up to their own; row i ranks the blocks 0..i with its own block's mass cleared,
+    keeps the prefix reaching `threshold` of the total (at most int(row_sparse * (i + 1)) blocks) with
+    ties, and always the first block; its own block stays only if the guard is 0.  "Blocks 0..i" are cut
+    to the seen[i] key blocks the row's chunk saw (the golden slices an array that holds only those), so for
+    a sequence whose trailing partial key group was dropped the cleared "own" block is the last one seen."""
+    rows = scores.shape[0]
+    mask = np.zeros(scores.shape, dtype=bool)
+    for i in range(rows):
+        if i <= 1:
+            mask[i, :i + 1] = True
+            continue
+        n = min(i + 1, int(seen[i]))
+        row = np.array(scores[i, :n], dtype=np.float64)
+        row[-1] = 0
+        order = (-np.sort(-row)).astype(np.float32)
+        cnt = int((order.cumsum(dtype=np.float32) < np.float32(threshold) * order.sum(dtype=np.float32)).sum()) + 1
+        if row_sparse > 0 and cnt > row_sparse * len(row):
+            cnt = int(row_sparse * len(row))
+        cnt = max(1, min(cnt, len(row)))
+        guard = order[cnt - 1]
+        keep = (row if golden_rounding else row.astype(np.float32)) >= guard
+        keep[0] = True
+        mask[i, :n] = keep
+    return mask, mask.sum(-1).astype(np.int32)
+
+
 def sparse_block_estimate(query, key, scale_value, threshold, row_sparse=1.0, block=128, stride=8,
-                          keep_sink=True, keep_recent=True, golden_rounding=False):
+                          keep_sink=True, keep_recent=True, golden_rounding=False, causal=False):
     """`sparse_estimate_cpu` for BNSD fp32 arrays [B, N, S, D] (key may have fewer heads).
     Returns (bool mask [B, N, blocks, blocks], int32 counts [B, N, blocks], float64 scores)."""
     b, n, s, _ = query.shape
@@ -100,8 +163,12 @@ def sparse_block_estimate(query, key, scale_value, threshold, row_sparse=1.0, bl
     score = np.zeros((b, n, blocks, blocks), dtype=np.float64)
     for bi in range(b):
         for ni in range(n):
-            sc = block_scores(query[bi, ni], key[bi, ni // group], scale_value, block, stride)
+            if causal:
+                sc, seen = block_scores_causal(query[bi, ni], key[bi, ni // group], scale_value, block, stride)
+                mask[bi, ni], count[bi, ni] = select_blocks_causal(sc, seen, threshold, row_sparse, golden_rounding)
+            else:
+                sc = block_scores(query[bi, ni], key[bi, ni // group], scale_value, block, stride)
+                mask[bi, ni], count[bi, ni] = select_blocks(sc, threshold, row_sparse, keep_sink, keep_recent,
+                                                             golden_rounding)
             score[bi, ni] = sc
-            mask[bi, ni], count[bi, ni] = select_blocks(sc, threshold, row_sparse, keep_sink, keep_recent,
-                                                         golden_rounding)
     return mask, count, score

@@ -1,8 +1,8 @@
 """Generates the fixtures in this directory by running MindIE-SD's own Python code on CPU.
 
-    python tests/golden/make_golden.py /path/to/MindIE-SD [rope]
+    python tests/golden/make_golden.py /path/to/MindIE-SD [rope|causal]
 
-(`rope` regenerates only the rotary-embedding fixture.)
+(`rope` regenerates only the rotary-embedding fixture, `causal` only the causal ada_bsa fixture.)
 
 The reference is imported with `torch_npu` replaced by a mock, exactly as its own CPU test runner
 does (tests/run.py:29-41 of MindIE-SD); only its pure-torch functions are called:
@@ -72,10 +72,33 @@ def make_rope(root):
     np.savez_compressed(HERE / "rope.npz", **out)
 
 
+def make_causal(root):
+    """The causal branches of the two ada_bsa goldens: the estimator's mask on the structured cases, and the
+    attention over a lower-triangular block mask that keeps the diagonal blocks."""
+    _, _, (_, est, ada) = import_reference(root)
+    out = {}
+    for (name, grid, heads, threshold, row_sparse, seed) in inputs.ESTIMATE_CASES:
+        q, k = inputs.structured_qk(seed, heads, grid, 128)
+        q, k = q.float().numpy(), k.float().numpy()
+        m = est.sparse_estimate_cpu(q, k, True, blocksize=128, stride=8, threshold=threshold, force_sparse=row_sparse)
+        out[f"{name}_shape"] = np.array(m.shape, dtype=np.int32)
+        out[f"{name}_bits"] = np.packbits(m.reshape(-1))
+        print("causal", name, m.shape, "density %.4f" % m.mean())
+    q, k, v = (inputs.randn(41 + i, 1, 2, 300, 128, dtype=torch.bfloat16) for i in range(3))
+    mask = torch.zeros(1, 2, 3, 32, dtype=torch.int8)
+    mask[..., :3] = torch.tril(torch.ones(3, 3, dtype=torch.int8))
+    mask[0, 1, 2, 1] = 0  # a hole below the diagonal
+    o = ada.ada_block_sparse_attention_cpu(q, k, v, mask, causal=True, blocksize=128)
+    out["attention_mask"] = mask.numpy()
+    out["attention_out"] = o.numpy()
+    np.savez_compressed(HERE / "ada_causal.npz", **out)
+
+
 def main(root):
     rf, attention_forward, (bsa, est, ada) = import_reference(root)
     torch.set_num_threads(8)
     make_rope(root)
+    make_causal(root)
 
     # 1. permutations: the reference applied to a tensor whose value is its own token index
     perm = {}
@@ -174,9 +197,9 @@ def main(root):
 
 
 if __name__ == "__main__":
-    if len(sys.argv) not in (2, 3) or (len(sys.argv) == 3 and sys.argv[2] != "rope"):
-        raise SystemExit("usage: python tests/golden/make_golden.py <path of a MindIE-SD source tree> [rope]")
+    if len(sys.argv) not in (2, 3) or (len(sys.argv) == 3 and sys.argv[2] not in ("rope", "causal")):
+        raise SystemExit("usage: python tests/golden/make_golden.py <path of a MindIE-SD source tree> [rope|causal]")
     if len(sys.argv) == 3:
-        make_rope(sys.argv[1])
+        {"rope": make_rope, "causal": make_causal}[sys.argv[2]](sys.argv[1])
     else:
         main(sys.argv[1])

@@ -77,8 +77,9 @@ def test_invalid_arguments_return_codes_without_a_gpu():
     e.head_dim, e.stride, e.sparse_size, e.scale, e.threshold = 128, 8, 128, 0.01, 0.9
     e.seq = 1001
     assert lib.mindiesd_sparse_block_estimate(ctypes.byref(e), None) == -2  # not a multiple of 8 tokens
-    e.seq, e.causal = 1024, 1
-    assert lib.mindiesd_sparse_block_estimate(ctypes.byref(e), None) == -5  # causal is not supported
+    e.seq, e.causal, e.causal_key_tokens = 1024, 1, 2000
+    assert lib.mindiesd_sparse_block_estimate(ctypes.byref(e), None) == -5  # more key tokens than tokens
+    e.causal = e.causal_key_tokens = 0
     assert lib.mindiesd_sparse_block_estimate_scratch_bytes(1, 40, 75600) == 4 * 9472 * (37 * 16 + 37) * 4
     with pytest.raises(_cabi.NativeLibraryError):
         _cabi.check(-2, "x")

@@ -87,8 +87,9 @@ def test_causal_with_block_mask():
     mask[..., torch.arange(nb), torch.arange(nb)] = 1  # the diagonal block is kept
     out = _cabi.attention(q.cuda(), k.cuda(), v.cuda(), block_mask=mask.cuda(), causal=True)
     keep = mask.bool().repeat_interleave(128, 2).repeat_interleave(128, 3)[:, :, :s, :s] & _causal_keep(s, s)
-    want = oa.attention_math(q, k, v, attn_mask=keep, head_first=True)
-    _check(out, want)
+    for n in range(2):  # the oracle takes one [q, kv] mask: a head at a time
+        want = oa.attention_math(q[:, n:n + 1], k[:, n:n + 1], v[:, n:n + 1], attn_mask=keep[0, n], head_first=True)
+        _check(out[:, n:n + 1], want)
     assert _cabi.device_status() == 0
 
 

@@ -142,6 +142,43 @@ def test_sparse_block_estimate_matches_reference():
         assert (plain & ~want).sum(-1).max() <= 1, name
 
 
+def test_sparse_block_estimate_causal_matches_reference():
+    """The causal branch of the restated estimator against the reference's numpy golden run with
+    causal=True (tests/golden/ada_causal.npz), bit for bit."""
+    z = np.load(G / "ada_causal.npz")
+    for (name, grid, heads, threshold, row_sparse, seed) in inputs.ESTIMATE_CASES:
+        q, k = inputs.structured_qk(seed, heads, grid, 128)
+        q, k = q.float().numpy(), k.float().numpy()
+        shape = tuple(z[f"{name}_shape"])
+        want = np.unpackbits(z[f"{name}_bits"])[:int(np.prod(shape))].reshape(shape).astype(bool)
+        got, count, _ = oada.sparse_block_estimate(q, k, 128 ** -0.5 / 8, threshold, row_sparse, golden_rounding=True,
+                                                   causal=True)
+        assert np.array_equal(got, want), (name, int((got != want).sum()))
+        assert np.array_equal(count, got.sum(-1)), name
+        assert not np.triu(got, 1).any(), name      # nothing above the diagonal
+        assert got[..., 0].all(), name              # the first block always stays
+        plain, _, _ = oada.sparse_block_estimate(q, k, 128 ** -0.5 / 8, threshold, row_sparse, causal=True)
+        assert not (want & ~plain).any(), name
+        assert (plain & ~want).sum(-1).max() <= 1, name
+
+
+def test_ada_attention_causal_golden_is_token_level_causality_when_the_diagonal_is_kept():
+    """ada_block_sparse_attention_cpu(causal=True) adds a triangle to the LAST kept columns of a row
+    (tests/plugin/test_adablocksparseattention.py:69-72).  For a mask that keeps every row's own block
+    that is ordinary token-level causality inside the kept blocks, which is what the oracle's
+    attention_math with a keep-mask computes."""
+    z = np.load(G / "ada_causal.npz")
+    q, k, v = (inputs.randn(41 + i, 1, 2, 300, 128, dtype=torch.bfloat16) for i in range(3))
+    mask = torch.from_numpy(z["attention_mask"])[..., :3]
+    want = torch.from_numpy(z["attention_out"])
+    tri = torch.tril(torch.ones(300, 300, dtype=torch.bool))
+    for n in range(2):
+        keep = mask[0, n].bool().repeat_interleave(128, 0).repeat_interleave(128, 1)[:300, :300] & tri
+        got = oa.attention_math(q[:, n:n + 1].float(), k[:, n:n + 1].float(), v[:, n:n + 1].float(), attn_mask=keep,
+                                head_first=True)
+        assert (got - want[:, n:n + 1]).abs().max().item() < 1e-4, n
+
+
 def test_ada_attention_golden_is_the_block_sparse_golden():
     z = np.load(G / "ada_attention.npz")
     q, k, v = (inputs.randn(41 + i, 1, 2, 300, 128, dtype=torch.bfloat16) for i in range(3))
