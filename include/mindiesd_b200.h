@@ -114,6 +114,24 @@ typedef struct mindiesd_attn_args {
     const int32_t* cu_seqlens_q;
     const int32_t* cu_seqlens_kv;
 
+    /* perm_t > 0: q, k, v and out are in the ORIGINAL token order of a (perm_t, perm_h, perm_w) latent grid
+       with perm_txt leading text tokens (seq_q == seq_kv == perm_txt + t*h*w), and the kernel applies the
+       RainFusion window permutation on the fly: its tiles -- and therefore the rows and columns of the block
+       mask / lists -- are those of the permuted order, its loads fetch each eight-token run of that order
+       from where it lies, and its output rows go back to their original positions.  This replaces the
+       four materialised permutations around the block-sparse call (rearrange_with_remaining of q, k, v and
+       inv_rearrange_with_remaining / _bsa_inv_rearrange of the output,
+       mindiesd/layers/flash_attn/sparse_flash_attn_rf_v2.py:137-289, sparse_flash_attn_rf_v3.py:22-97).
+       Needs w and perm_txt to be multiples of 8 (MINDIESD_E_SHAPE otherwise: use mindiesd_rf_rearrange),
+       two-byte operands, no packed sequences.
+       perm_inputs_permuted != 0: q, k and v are ALREADY in the permuted order (mindiesd_rf_rearrange) and only
+       the output is written back in the original order -- the inverse permutation costs nothing then, and
+       any grid is accepted.  Fetching the permuted order on the fly costs 32 small copies per 128-token tile
+       instead of 2 large ones: measured at the 21x45x80 grid it is slower than permuting q, k and v once, so
+       the layer API permutes the inputs and lets the kernel undo the permutation of the output. */
+    int32_t perm_t, perm_h, perm_w, perm_txt;
+    int32_t perm_inputs_permuted;
+
     /* Time limit of every bounded wait inside the kernel, microseconds; 0 = the default (1 s).  A wait
        that runs out makes its thread block unwind, fill its output rows with NaN and set the device
        status word (mindiesd_device_status). */

@@ -1,6 +1,7 @@
 // extern "C" entry points: attention forward, status word, ABI version.
 #include "capi_common.h"
 #include "fa_fwd.h"
+#include "rf_grid.cuh"
 
 #include <mutex>
 
@@ -239,6 +240,26 @@ extern "C" int mindiesd_attention_fwd(const mindiesd_attn_args* a, void* stream)
         p.cu_seqlens_q = a->cu_seqlens_q;
         p.cu_seqlens_kv = a->cu_seqlens_kv;
         p.num_seqs = a->num_seqs;
+    }
+    if (a->perm_t != 0) {
+        if (a->perm_t < 0 || a->perm_h <= 0 || a->perm_w <= 0 || a->perm_txt < 0) return MINDIESD_E_SHAPE;
+        const Grid g = make_grid(a->perm_t, a->perm_h, a->perm_w, a->perm_txt);
+        if (a->seq_q != g.img + g.txt) return MINDIESD_E_SHAPE;
+        if (a->num_seqs > 0) return MINDIESD_E_VALUE;
+        if (a->perm_inputs_permuted) {
+            p.perm_on = 2;
+        } else {
+            if (!groups_of_eight_are_contiguous(g) || a->seq_kv != a->seq_q) return MINDIESD_E_SHAPE;
+            if (fp8) return MINDIESD_E_VALUE;
+            if ((rc = encode_tile_map(&p.tm_q8, a->q, a->in_dtype, 128, a->seq_q, a->heads, a->batch, a->q_stride, 8))) return rc;
+            if ((rc = encode_tile_map(&p.tm_k8, a->k, a->in_dtype, 128, a->seq_kv, a->kv_heads, a->batch, a->k_stride, 8))) return rc;
+            if ((rc = encode_tile_map(&p.tm_v8, a->v, a->in_dtype, 128, a->seq_kv, a->kv_heads, a->batch, a->v_stride, 8))) return rc;
+            p.perm_on = 1;
+        }
+        p.perm_t = a->perm_t;
+        p.perm_h = a->perm_h;
+        p.perm_w = a->perm_w;
+        p.perm_txt = a->perm_txt;
     }
     p.wait_limit_us = a->wait_limit_us ? a->wait_limit_us : kDefaultWaitLimitUs;
     p.test_withhold = a->test_withhold;

@@ -16,11 +16,25 @@
 // has work of one tile while the other tile's rows are in the exponent unit.
 #include "fa_fwd.h"
 #include "ptx_sm100.cuh"
+#include "rf_grid.cuh"
 
 #include <cuda_bf16.h>
 #include <type_traits>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
+
+// Development aid, off in every shipped build: with -DSDB_FA_TRACE one thread block records clock64()
+// stamps of its roles for key blocks 200..231 into the buffer passed as `lse` (which is then not
+// written as a log-sum-exp): [role][block - 200][slot], role 0/1 = softmax of tile 0/1, 2 = MMA thread.
+#ifdef SDB_FA_TRACE
+#define SDB_TR(role, idx, slot)                                                                                  \
+    do {                                                                                                         \
+        if (blockIdx.x == 40 && blockIdx.y == 0 && blockIdx.z == 0 && p.lse != nullptr && (idx) >= 200 && (idx) < 232) \
+            reinterpret_cast<long long*>(p.lse)[((role) * 32 + ((idx) - 200)) * 16 + (slot)] = clock64();          \
+    } while (0)
+#else
+#define SDB_TR(role, idx, slot) do { } while (0)
+#endif
 
 namespace sdb {
 
@@ -51,6 +65,17 @@ constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) compiles to:
 //      keys; the row sum is taken after the hand-over, off the path the MMA thread waits on
 #ifndef SDB_FA_RESPLIT_FP8
 #define SDB_FA_RESPLIT_FP8 0
+#endif
+// Of the eight groups of four scores in a 32-column chunk, how many take the exponentials of their
+// second pair on the FMA pipe (ex2_poly2) instead of the exponent unit: 8 = half of all exponentials.
+#ifndef SDB_FA_POLY
+#define SDB_FA_POLY 0
+#endif
+#ifndef SDB_FA_POLY_FP8
+#define SDB_FA_POLY_FP8 SDB_FA_POLY
+#endif
+#ifndef SDB_FA_DEFER_SUM_FP8
+#define SDB_FA_DEFER_SUM_FP8 0
 #endif
 #ifndef SDB_FA_BF16_MODE
 #define SDB_FA_BF16_MODE 0
@@ -211,7 +236,9 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     // The decision is taken once per thread block: all of its threads stay or all leave (the ones that stay
     // set up barriers and tensor memory for the others).  A block that leaves marks its rows.
     if (__syncthreads_or(tid == 0 && p.status && *reinterpret_cast<volatile int*>(p.status) != 0)) {
-        if (tid < 2 * kTile && q_row0 + tid < q_len) poison_row(p, batch, head, q_base + q_row0 + tid);
+        if (tid < 2 * kTile && q_row0 + tid < q_len)
+            poison_row(p, batch, head, q_base + (p.perm_on ? source_of(make_grid(p.perm_t, p.perm_h, p.perm_w, p.perm_txt), q_row0 + tid)
+                                                           : q_row0 + tid));
         return;
     }
     const uint32_t wait_us = p.wait_limit_us;
@@ -300,7 +327,49 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     // each softmax warpgroup takes its share.
     if (warp >= 8) {
       if constexpr (kResplit) warpgroup_reg_dec<kRegsOther>();
-      if (warp == kLoadWarp) {
+      if (warp == kLoadWarp && p.perm_on == 1) {
+        // ---- TMA producer, RainFusion window permutation applied on the fly ---------------------
+        // q, k and v are in their original token order; the tiles the other roles see hold the PERMUTED
+        // order.  Eight consecutive positions of the permuted order are eight consecutive source tokens
+        // (the launcher checked that the grid allows it), so a 128-row tile is 16 copies of 8 tokens per
+        // 64-channel atom: each lane of the warp owns one (group, atom) and issues one 1 KB copy per tile.
+        if constexpr (!kFp8) {
+            const Grid grid = make_grid(p.perm_t, p.perm_h, p.perm_w, p.perm_txt);
+            const int grp = lane & 15, atom = lane >> 4;
+            // first source token of the eight-row group at position pos; past the end: out of range, which
+            // the copy engine fills with zeros
+            auto group_token = [&](int pos, int len) { return pos < len ? source_of(grid, pos) : len; };
+            const uint32_t my_off = static_cast<uint32_t>(atom * C::kAtomBytes + grp * 1024);
+            if (lane == 0) mbar_arrive_expect_tx(bar_q(), (tile1_valid ? 2 : 1) * C::kTileBytes);
+            __syncwarp();
+            for (int t = 0; t < (tile1_valid ? 2 : 1); ++t)
+                tma_load_4d(smem_u32(sm_q + t * C::kTileBytes) + my_off, &p.tm_q8, bar_q(), atom * C::kBoxInner,
+                            group_token(q_row0 + t * kTile + grp * 8, q_len), head, batch);
+            Ring ring;
+            int issued = 0;
+            bool ok = true;
+            for (int u = next_block(0); u >= 0 && ok; u = next_block(u + 1)) {
+                const int tok = group_token(u * kTile + grp * 8, k_len);
+                for (int which = 0; which < 2 && ok; ++which) {  // 0: K block, 1: V block
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_empty(ring.idx), ring.phase ^ 1u, abort_flag, 1, wait_us));
+                    if (!ok) break;
+                    if (lane == 0) mbar_arrive_expect_tx(bar_full(ring.idx), C::kTileBytes);
+                    __syncwarp();
+                    tma_load_4d(smem_u32(sm_ring + ring.idx * C::kTileBytes) + my_off, which ? &p.tm_v8 : &p.tm_k8,
+                                bar_full(ring.idx), atom * C::kBoxInner, tok, kv_head, batch);
+                    ring.template next<C::kStages>();
+                    ++issued;
+                }
+            }
+            // Before the CTA may exit, every copy this warp started must have landed.
+            mbar_wait_drain(bar_q(), 0);
+            const int pending = issued < C::kStages ? issued : C::kStages;
+            for (int i = 0; i < pending; ++i) {
+                const int n = issued - 1 - i;
+                mbar_wait_drain(bar_full(n % C::kStages), static_cast<uint32_t>(n / C::kStages) & 1u);
+            }
+        }
+      } else if (warp == kLoadWarp) {
         // ---- TMA producer ---------------------------------------------------------------------
         if (lane == 0) {
             const uint32_t q_bytes = (tile1_valid ? 2 : 1) * C::kTileBytes;
@@ -401,20 +470,25 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
 
                 ok = mbar_wait(bar_full(vslot.idx), vslot.phase, abort_flag, 12, wait_us);
                 if (!ok) break;
+                SDB_TR(2, u, 0);
                 if (f & 1) {
                     if constexpr (kSplit) {
                         ok = mbar_wait(bar_p(0, 0), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13, wait_us);
                         if (!ok) break;
                         tc_fence_after();
+                        SDB_TR(2, u, 1);
                         issue_pv(0, 0, vslot.idx, pv_cnt[0] > 0);
+                        SDB_TR(2, u, 2);
                         if constexpr (kHalves && !kFp8) umma_commit(bar_h(0));
                     }
                     ok = mbar_wait(bar_p(0, 1), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13, wait_us);
                     if (!ok) break;
                     tc_fence_after();
+                    SDB_TR(2, u, 3);
                     if constexpr (!kSplit) issue_pv(0, 0, vslot.idx, pv_cnt[0] > 0);
                     issue_pv(0, 1, vslot.idx, true);
                     ++pv_cnt[0];
+                    SDB_TR(2, u, 4);
                 }
                 if (nf) {
                     ok = mbar_wait(bar_full(kslot.idx), kslot.phase, abort_flag, 17, wait_us);
@@ -422,23 +496,29 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     tc_fence_after();
                 }
                 if (nf & 1) issue_s(0, kslot.idx);
+                SDB_TR(2, u, 5);
                 if (f & 2) {
                     if constexpr (kSplit) {
                         ok = mbar_wait(bar_p(1, 0), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14, wait_us);
                         if (!ok) break;
                         tc_fence_after();
+                        SDB_TR(2, u, 6);
                         issue_pv(1, 0, vslot.idx, pv_cnt[1] > 0);
+                        SDB_TR(2, u, 7);
                         if constexpr (kHalves && !kFp8) umma_commit(bar_h(1));
                     }
                     ok = mbar_wait(bar_p(1, 1), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14, wait_us);
                     if (!ok) break;
                     tc_fence_after();
+                    SDB_TR(2, u, 8);
                     if constexpr (!kSplit) issue_pv(1, 0, vslot.idx, pv_cnt[1] > 0);
                     issue_pv(1, 1, vslot.idx, true);
                     ++pv_cnt[1];
+                    SDB_TR(2, u, 9);
                 }
                 umma_commit(bar_empty(vslot.idx));
                 if (nf & 2) issue_s(1, kslot.idx);
+                SDB_TR(2, u, 10);
                 if (nf) umma_commit(bar_empty(kslot.idx));
                 u = nu;
             }
@@ -498,11 +578,13 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             ok = __all_sync(0xffffffffu, mbar_wait(bar_s(t), static_cast<uint32_t>(cnt) & 1u, abort_flag, 20 + t, wait_us));
             if (!ok) break;
             tc_fence_after();
+            if (row_in_tile == 64) SDB_TR(t, j, 0);
 
             uint32_t s[4][32];
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld32(taddr_s + c * 32, s[c]);
             tmem_wait_ld();
+            if (row_in_tile == 64) SDB_TR(t, j, 1);
 
             float mult = p.scale_log2;
             float v_off = 0.0f, l_fix = 1.0f;
@@ -530,6 +612,23 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                         if (c * 32 + i >= n_seen) s[c][i] = 0xff800000u;  // -inf
             };
             if (masked) mask_scores();
+            // The four exponentials of one group: x = s * mult - m as packed pairs, the first pair on the
+            // exponent unit, the second there too or -- for kPoly of every eight groups -- on the FMA pipe.
+            constexpr int kPoly = kFp8 ? SDB_FA_POLY_FP8 : SDB_FA_POLY;
+            auto exp4 = [&](auto clamp_high, int c, int i, uint64_t mult2, uint64_t negm2, float& e0, float& e1, float& e2,
+                            float& e3) {
+                unpack2(fma2(pack2(__uint_as_float(s[c][4 * i]), __uint_as_float(s[c][4 * i + 1])), mult2, negm2), e0, e1);
+                e0 = ex2_approx(e0);
+                e1 = ex2_approx(e1);
+                const uint64_t x23 = fma2(pack2(__uint_as_float(s[c][4 * i + 2]), __uint_as_float(s[c][4 * i + 3])), mult2, negm2);
+                if (((i + 1) * kPoly) / 8 > (i * kPoly) / 8) {  // resolved at compile time: i is an unrolled index
+                    ex2_poly2<decltype(clamp_high)::value>(x23, e2, e3);
+                } else {
+                    unpack2(x23, e2, e3);
+                    e2 = ex2_approx(e2);
+                    e3 = ex2_approx(e3);
+                }
+            };
             auto row_max = [&]() {
                 // Eight independent chains of three-input max: a single running max would be 128 dependent
                 // instructions.
@@ -663,12 +762,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             float e0, e1, e2, e3;
-                            unpack2(fma2(pack2(__uint_as_float(s[c][4 * i]), __uint_as_float(s[c][4 * i + 1])), mult2, negm2), e0, e1);
-                            e0 = ex2_approx(e0);
-                            e1 = ex2_approx(e1);
-                            unpack2(fma2(pack2(__uint_as_float(s[c][4 * i + 2]), __uint_as_float(s[c][4 * i + 3])), mult2, negm2), e2, e3);
-                            e2 = ex2_approx(e2);
-                            e3 = ex2_approx(e3);
+                            exp4(std::true_type{}, c, i, mult2, negm2, e0, e1, e2, e3);  // speculative: x has no upper bound
                             sum2[0] = add2(sum2[0], pack2(e0, e1));
                             sum2[1] = add2(sum2[1], pack2(e2, e3));
                             pk[c][2 * i] = pack_pair(e0, e1, kIn);
@@ -736,26 +830,31 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                         }
                     }
                 }
+                if (row_in_tile == 64) SDB_TR(t, j, 2);
                 // x = s * mult - m as packed pairs (one instruction per two scores), then ex2 and pack.
                 const float neg_m = m_run == -INFINITY ? 0.0f : (kFp8 ? (kFp8PShiftLog2 + v_off - m_run) : -m_run);
                 const uint64_t mult2 = pack2(mult, mult), negm2 = pack2(neg_m, neg_m);
+                // Two-byte operands take the row sum after the hand-over (the exponentials stay in the
+                // scores' registers until then); e4m3 -- whose loop is bound by the exponent unit, with
+                // issue slots to spare -- sums as it goes, which keeps fewer values alive.
+                constexpr bool kDeferSum = SDB_FA_DEFER_SUM_FP8 || !kFp8;
+                uint64_t run2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
     #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t pk[kFp8 ? 8 : 16];
     #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         float e0, e1, e2, e3;
-                        unpack2(fma2(pack2(__uint_as_float(s[c][4 * i]), __uint_as_float(s[c][4 * i + 1])), mult2, negm2), e0, e1);
-                        e0 = ex2_approx(e0);
-                        e1 = ex2_approx(e1);
-                        unpack2(fma2(pack2(__uint_as_float(s[c][4 * i + 2]), __uint_as_float(s[c][4 * i + 3])), mult2, negm2), e2, e3);
-                        e2 = ex2_approx(e2);
-                        e3 = ex2_approx(e3);
-                        // kept in place of the scores: the row sum is taken after the hand-over
-                        s[c][4 * i] = __float_as_uint(e0);
-                        s[c][4 * i + 1] = __float_as_uint(e1);
-                        s[c][4 * i + 2] = __float_as_uint(e2);
-                        s[c][4 * i + 3] = __float_as_uint(e3);
+                        exp4(std::false_type{}, c, i, mult2, negm2, e0, e1, e2, e3);  // x <= the lag: the max was taken first
+                        if constexpr (kDeferSum) {
+                            s[c][4 * i] = __float_as_uint(e0);
+                            s[c][4 * i + 1] = __float_as_uint(e1);
+                            s[c][4 * i + 2] = __float_as_uint(e2);
+                            s[c][4 * i + 3] = __float_as_uint(e3);
+                        } else {
+                            run2[0] = add2(run2[0], pack2(e0, e1));
+                            run2[1] = add2(run2[1], pack2(e2, e3));
+                        }
                         if constexpr (kFp8) {
                             pk[i] = pack_quad_e4m3(e0, e1, e2, e3);
                         } else {
@@ -766,14 +865,20 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     // The packed chunk lands on columns whose scores are already in registers.
                     if constexpr (kFp8) tmem_st8(taddr_s + c * 8, pk);
                     else tmem_st16(taddr_s + c * 16, pk);
+                    if (row_in_tile == 64) SDB_TR(t, j, 3 + c);
                     if (c == kFirstChunks - 1 || c == 3) {  // a part of the block's keys is complete: hand it over
                         tmem_wait_st();
                         tc_fence_before();
                         mbar_arrive(bar_p(t, c == 3 ? 1 : 0));
+                        if (row_in_tile == 64) SDB_TR(t, j, c == 3 ? 8 : 7);
                     }
                 }
-                // The row sum, while the MMA thread is busy with what it was just handed.
-                {
+                if constexpr (!kDeferSum) {
+                    float a, b;
+                    unpack2(add2(run2[0], run2[1]), a, b);
+                    l_run += (a + b) * l_fix;
+                } else {
+                    // The row sum, while the MMA thread is busy with what it was just handed.
                     uint64_t sum2[4] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f), pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
     #pragma unroll
                     for (int c = 0; c < 4; ++c)
@@ -784,6 +889,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     unpack2(add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3])), a, b);
                     l_run += (a + b) * l_fix;
                 }
+                if (row_in_tile == 64) SDB_TR(t, j, 9);
             }
             ++cnt;
         }
@@ -791,13 +897,17 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         if (ok && (t == 0 || tile1_valid)) {  // warp-uniform: the tensor-memory loads are warp-collective
             tc_fence_after();
             const bool row_ok = q_row < q_len;
+            // Row of the output this thread writes: its own position, or -- window permutation on the fly --
+            // the source token that position holds, so that the output is in the original order.
+            int out_row = q_row;
+            if (p.perm_on && row_ok) out_row = source_of(make_grid(p.perm_t, p.perm_h, p.perm_w, p.perm_txt), q_row);
             // l_run carries the 2^8 shift of the stored e4m3 probabilities, so it cancels in O / l.
             const float inv_l = l_run > 0.0f ? v_ref / l_run : 0.0f;
             const float* v_ch = (kFp8 && p.v_scale_block == 0)
                                     ? p.v_scale + (static_cast<int64_t>(batch) * p.kv_heads + kv_head) * kHeadDim
                                     : nullptr;
             uint8_t* orow = static_cast<uint8_t*>(p.out) +
-                            (batch * p.o_stride[0] + head * p.o_stride[1] + static_cast<int64_t>(q_base + q_row) * p.o_stride[2]) *
+                            (batch * p.o_stride[0] + head * p.o_stride[1] + static_cast<int64_t>(q_base + out_row) * p.o_stride[2]) *
                                 (p.out_dtype == 2 ? 4 : 2);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -837,11 +947,13 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     }
                 }
             }
+#ifndef SDB_FA_TRACE
             if (p.lse && row_ok) {
                 const float shift = kFp8 ? kFp8PShiftLog2 : 0.0f;
-                p.lse[batch * p.lse_stride[0] + head * p.lse_stride[1] + (q_base + q_row) * p.lse_stride[2]] =
+                p.lse[batch * p.lse_stride[0] + head * p.lse_stride[1] + (q_base + out_row) * p.lse_stride[2]] =
                     l_run > 0.0f ? (m_run - shift) * 0.6931471805599453f + logf(l_run) : -INFINITY;
             }
+#endif
         }
     }
 
@@ -852,7 +964,9 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
-    if (*abort_flag && tid < 2 * kTile && q_row0 + tid < q_len) poison_row(p, batch, head, q_base + q_row0 + tid);
+    if (*abort_flag && tid < 2 * kTile && q_row0 + tid < q_len)
+        poison_row(p, batch, head, q_base + (p.perm_on ? source_of(make_grid(p.perm_t, p.perm_h, p.perm_w, p.perm_txt), q_row0 + tid)
+                                                       : q_row0 + tid));
     if (tid == 0 && *abort_flag && p.status) {
         // First CTA to report wins the word and leaves where it stopped behind it.
         if (atomicCAS(p.status, 0, kStatusFaWaitGaveUp) == 0) {

@@ -19,6 +19,13 @@ struct FaParams {
     alignas(64) CUtensorMap tm_q;
     alignas(64) CUtensorMap tm_k;
     alignas(64) CUtensorMap tm_v;
+    // RainFusion window permutation inside the kernel.  perm_on 1: q, k, v and out are in their original
+    // token order, the kernel walks the permuted order (maps with a box of 128 bytes x 8 tokens below).
+    // perm_on 2: q, k, v are already permuted; only the output rows go back to their original positions.
+    alignas(64) CUtensorMap tm_q8;
+    alignas(64) CUtensorMap tm_k8;
+    alignas(64) CUtensorMap tm_v8;
+    int perm_on, perm_t, perm_h, perm_w, perm_txt;
     void* out;
     float* lse;
     int64_t lse_stride[3];  // element strides of batch, head, token

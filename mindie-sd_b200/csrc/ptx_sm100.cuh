@@ -263,6 +263,41 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
     return d;
 }
 
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// 2^x for a packed pair on the FMA and integer pipes, leaving the exponent unit (16 results per clock
+// per SM) to other values: x = n + f with n = round(x) taken from the low mantissa bits of x + 1.5 * 2^23,
+// a cubic for 2^f on [-0.5, 0.5] (relative error 7.5e-5, well inside the rounding of a two-byte or
+// e4m3 probability), and n added to the exponent field.  x is clamped to [lo, hi] inside [-125, 126]
+// so that the exponent arithmetic cannot wrap; -inf (a masked score) gives 2^lo, i.e. nothing.
+template <bool kClampHigh>
+__device__ __forceinline__ void ex2_poly2(uint64_t x2, float& e0, float& e1) {
+    float x0, x1;
+    unpack2(x2, x0, x1);
+    x0 = fmaxf(x0, -125.0f);
+    x1 = fmaxf(x1, -125.0f);
+    if constexpr (kClampHigh) {
+        x0 = fminf(x0, 126.0f);
+        x1 = fminf(x1, 126.0f);
+    }
+    const uint64_t x = pack2(x0, x1);
+    const uint64_t magic = pack2(12582912.0f, 12582912.0f);
+    const uint64_t t = add2(x, magic);
+    const uint64_t f = sub2(x, sub2(t, magic));
+    uint64_t p = fma2(pack2(0.055171650f, 0.055171650f), f, pack2(0.24261113f, 0.24261113f));
+    p = fma2(p, f, pack2(0.69326097f, 0.69326097f));
+    p = fma2(p, f, pack2(0.99992806f, 0.99992806f));
+    uint32_t plo, phi, tlo, thi;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(plo), "=r"(phi) : "l"(p));
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(tlo), "=r"(thi) : "l"(t));
+    e0 = __uint_as_float(plo + (tlo << 23));
+    e1 = __uint_as_float(phi + (thi << 23));
+}
+
 // Three-input maximum (one instruction on this architecture).
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;

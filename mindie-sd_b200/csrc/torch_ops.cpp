@@ -66,6 +66,8 @@ struct SparseSpec {
 // What only some operators pass on: the causal triangle, where the log-sum-exp goes, packed sequences.
 struct AttnExtra {
     bool causal = false;
+    int perm[4] = {0, 0, 0, 0};  // (t, h, w, txt_len): the window permutation applied inside the kernel
+    bool perm_inputs_permuted = false;  // q, k, v already permuted: only the output goes back
     int64_t lse_stride[3] = {0, 0, 0};   // elements: batch, head, token; all zero = contiguous [B, N, S]
     const at::Tensor* cu_seqlens_q = nullptr;  // int32 [num_seqs + 1] on the device (q, k, v then have batch 1)
     const at::Tensor* cu_seqlens_kv = nullptr;
@@ -129,6 +131,11 @@ void run_attention(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v
         a.v_scale_block = v_block;
     }
     a.causal = extra.causal ? 1 : 0;
+    a.perm_t = extra.perm[0];
+    a.perm_h = extra.perm[1];
+    a.perm_w = extra.perm[2];
+    a.perm_txt = extra.perm[3];
+    a.perm_inputs_permuted = extra.perm_inputs_permuted ? 1 : 0;
     for (int i = 0; i < 3; ++i) a.lse_stride[i] = extra.lse_stride[i];
     if (extra.cu_seqlens_q) {
         const at::Tensor& cq = *extra.cu_seqlens_q;
@@ -143,6 +150,17 @@ void run_attention(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v
     }
     c10::cuda::CUDAGuard guard(q.device());
     check_rc(mindiesd_attention_fwd(&a, stream_of(q)), "mindiesd_attention_fwd");
+}
+
+// Head dims below 128 (the reference's own shape list is mostly 40, 64, 88, 96: tests/plugin/test_la.csv) run
+// on the 128-wide kernel with zero channels appended: zeros add nothing to q k^T and the extra output
+// channels are cut off.  It costs a padded copy of q, k, v -- the reference's laser attention pads the
+// same way (mindiesd/layers/flash_attn/ascend_laser_attention.py:38-75).
+at::Tensor pad_head_dim(const at::Tensor& x) {
+    const int64_t d = x.size(-1);
+    if (d == 128) return x;
+    TORCH_CHECK(d > 0 && d < 128, "mindiesd: head dim must be at most 128, got ", d);
+    return at::constant_pad_nd(x, {0, 128 - d}, 0);
 }
 
 // ---- la: dense attention, fp32 output + log-sum-exp -----------------------------------------------
@@ -161,8 +179,11 @@ std::tuple<at::Tensor, at::Tensor> la_cuda(const at::Tensor& query, const at::Te
     TORCH_CHECK(keep_prob == 1.0, "la: keep_prob must be 1.0");
     (void)head_num; (void)pre_tokens; (void)next_tokens; (void)is_highPrecision;
     at::Tensor lse = at::empty({query.size(0), query.size(1), query.size(2)}, query.options().dtype(at::kFloat));
-    at::Tensor out = at::empty(query.sizes(), query.options().dtype(at::kFloat));
-    run_attention(query, key, value, out, lse.data_ptr<float>(), true, scale_value, SparseSpec{});
+    const int64_t d = query.size(3);
+    at::Tensor q = pad_head_dim(query), k = pad_head_dim(key), v = pad_head_dim(value);
+    at::Tensor out = at::empty(q.sizes(), q.options().dtype(at::kFloat));
+    run_attention(q, k, v, out, lse.data_ptr<float>(), true, scale_value, SparseSpec{});
+    if (d != 128) out = out.narrow(3, 0, d).contiguous();
     return std::make_tuple(lse, out);
 }
 
@@ -415,12 +436,64 @@ at::Tensor ada_block_sparse_attention_cuda(const at::Tensor& query, const at::Te
 // ---- dense attention in the caller's layout ---------------------------------------------------------
 at::Tensor attention_fwd_cuda(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, double scale,
                               bool head_first, bool causal) {
-    at::Tensor out = at::empty_like(query);
-    if (!out.is_contiguous() && out.stride(3) != 1) out = at::empty(query.sizes(), query.options());
     AttnExtra ex;
     ex.causal = causal;
+    if (query.dim() == 4 && query.size(3) != 128) {
+        const int64_t d = query.size(3);
+        at::Tensor q = pad_head_dim(query), k = pad_head_dim(key), v = pad_head_dim(value);
+        at::Tensor wide = at::empty(q.sizes(), q.options());
+        run_attention(q, k, v, wide, nullptr, head_first, scale, SparseSpec{}, -1, -1, nullptr, nullptr, nullptr, 0, 0, ex);
+        return wide.narrow(3, 0, d).contiguous();
+    }
+    at::Tensor out = at::empty_like(query);
+    if (!out.is_contiguous() && out.stride(3) != 1) out = at::empty(query.sizes(), query.options());
     run_attention(query, key, value, out, nullptr, head_first, scale, SparseSpec{}, -1, -1, nullptr, nullptr, nullptr, 0, 0,
                   ex);
+    return out;
+}
+
+// ---- RainFusion block-sparse attention on un-permuted tensors ---------------------------------------------
+// Mask (or lists) in the block order of the window permutation; the output comes back in the original token
+// order without a copy of its own.  inputs_permuted: q, k, v were permuted beforehand (rf_rearrange);
+// otherwise they are in their original order and the kernel fetches the permuted order itself.
+at::Tensor rf_sparse_attention_cuda(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
+                                    const c10::optional<at::Tensor>& block_mask,
+                                    const c10::optional<at::Tensor>& select_idx,
+                                    const c10::optional<at::Tensor>& select_num_idx, at::IntArrayRef latent_shape,
+                                    int64_t txt_len, double scale, std::string input_layout, bool inputs_permuted) {
+    TORCH_CHECK(input_layout == "BNSD" || input_layout == "BSND", "rf_sparse_attention: input_layout must be 'BNSD' or 'BSND'");
+    TORCH_CHECK(latent_shape.size() == 3, "rf_sparse_attention: latent_shape must be (t, h, w)");
+    TORCH_CHECK(inputs_permuted || (latent_shape[2] % 8 == 0 && txt_len % 8 == 0 && txt_len >= 0),
+                "rf_sparse_attention: fetching the permuted order inside the kernel needs the grid width and the text "
+                "length to be multiples of 8");
+    TORCH_CHECK(block_mask.has_value() != (select_idx.has_value() && select_num_idx.has_value()),
+                "rf_sparse_attention: pass either block_mask or select_idx and select_num_idx");
+    const bool head_first = input_layout == "BNSD";
+    at::Tensor out = at::empty(query.sizes(), query.options());
+    SparseSpec sp;
+    at::Tensor sel, num;
+    if (block_mask.has_value()) {
+        sp.mode = MINDIESD_SPARSE_MASK;
+        sp.mask = &block_mask.value();
+    } else {
+        sel = select_idx.value().contiguous();
+        num = select_num_idx.value().contiguous();
+        const int64_t blocks = (query.size(head_first ? 2 : 1) + 127) / 128;
+        TORCH_CHECK(sel.is_cuda() && sel.scalar_type() == at::kLong && sel.dim() == 3 && sel.size(0) == blocks &&
+                        sel.size(2) == blocks && num.is_cuda() && num.scalar_type() == at::kLong && num.dim() == 2 &&
+                        num.size(0) == blocks,
+                    "rf_sparse_attention: select_idx must be int64 [blocks, N, blocks], select_num_idx int64 [blocks, N]");
+        sp.mode = MINDIESD_SPARSE_LIST;
+        sp.select_idx = &sel;
+        sp.select_num = &num;
+    }
+    AttnExtra ex;
+    ex.perm[0] = static_cast<int>(latent_shape[0]);
+    ex.perm[1] = static_cast<int>(latent_shape[1]);
+    ex.perm[2] = static_cast<int>(latent_shape[2]);
+    ex.perm[3] = static_cast<int>(txt_len);
+    ex.perm_inputs_permuted = inputs_permuted;
+    run_attention(query, key, value, out, nullptr, head_first, scale, sp, -1, -1, nullptr, nullptr, nullptr, 0, 0, ex);
     return out;
 }
 
@@ -710,6 +783,10 @@ TORCH_LIBRARY(mindiesd, m) {
     // torch_npu calls or eager torch code.
     m.def("attention_fwd(Tensor query, Tensor key, Tensor value, float scale, bool head_first, bool causal=False) -> Tensor");
     m.def(
+        "rf_sparse_attention(Tensor query, Tensor key, Tensor value, Tensor? block_mask, Tensor? select_idx, "
+        "Tensor? select_num_idx, int[] latent_shape, int txt_len, float scale, str input_layout, "
+        "bool inputs_permuted=False) -> Tensor");
+    m.def(
         "attention_varlen_fwd(Tensor query, Tensor key, Tensor value, Tensor cu_seqlens_q, Tensor cu_seqlens_k, "
         "float scale, bool causal=False) -> Tensor");
     m.def("rf_rearrange(Tensor x, int[] latent_shape, int txt_len, str input_layout, bool inverse) -> Tensor");
@@ -736,6 +813,7 @@ TORCH_LIBRARY_IMPL(mindiesd, CUDA, m) {
     m.impl("sparse_block_estimate", &sparse_block_estimate_cuda);
     m.impl("attention_fwd", &attention_fwd_cuda);
     m.impl("attention_varlen_fwd", &attention_varlen_fwd_cuda);
+    m.impl("rf_sparse_attention", &rf_sparse_attention_cuda);
     m.impl("rf_rearrange", &rf_rearrange_cuda);
     m.impl("rf_block_mask", &rf_block_mask_cuda);
     m.impl("rf_pool", &rf_pool_cuda);

@@ -48,6 +48,8 @@ class AttnArgs(C.Structure):
         ("lse_stride", C.c_int64 * 3),
         ("causal", C.c_int32), ("num_seqs", C.c_int32),
         ("cu_seqlens_q", C.c_void_p), ("cu_seqlens_kv", C.c_void_p),
+        ("perm_t", C.c_int32), ("perm_h", C.c_int32), ("perm_w", C.c_int32), ("perm_txt", C.c_int32),
+        ("perm_inputs_permuted", C.c_int32),
         ("wait_limit_us", C.c_uint32), ("test_withhold", C.c_int32),
     ]
 
@@ -247,7 +249,7 @@ def _dims(x, head_first):
 def attention(q, k, v, head_first=True, scale=None, block_mask=None, select_idx=None, select_num=None,
               out_dtype=None, want_lse=False, q_scale=None, k_scale=None, v_scale=None, k_scale_block=0,
               v_scale_block=0, out=None, causal=False, cu_seqlens_q=None, cu_seqlens_kv=None, wait_limit_us=0,
-              test_withhold=0):
+              test_withhold=0, perm_grid=None, perm_txt=0, perm_inputs_permuted=False):
     """mindiesd_attention_fwd on the current stream.  Returns out, or (out, lse) when want_lse.
     cu_seqlens_q / cu_seqlens_kv (int32 device tensors [num_seqs + 1]) select the packed
     variable-length form: q, k, v are then [1, N, T, D] (head_first) or [1, T, N, D]."""
@@ -287,6 +289,10 @@ def attention(q, k, v, head_first=True, scale=None, block_mask=None, select_idx=
                 raise NativeLibraryError(f"{name} must be a contiguous int32 tensor on the device of q")
         a.num_seqs = cu_seqlens_q.numel() - 1
         a.cu_seqlens_q, a.cu_seqlens_kv = cu_seqlens_q.data_ptr(), cu_seqlens_kv.data_ptr()
+    if perm_grid is not None:  # the RainFusion window permutation applied inside the kernel
+        a.perm_t, a.perm_h, a.perm_w = (int(x) for x in perm_grid)
+        a.perm_txt = int(perm_txt)
+        a.perm_inputs_permuted = int(bool(perm_inputs_permuted))
     a.wait_limit_us, a.test_withhold = int(wait_limit_us), int(test_withhold)
     check(lib().mindiesd_attention_fwd(C.byref(a), current_stream_ptr(q.device)), "mindiesd_attention_fwd")
     return (out, lse) if want_lse else out

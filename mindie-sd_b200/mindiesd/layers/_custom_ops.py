@@ -135,6 +135,12 @@ def _attention_fwd_fake(query, key, value, scale, head_first, causal=False):
     return torch.empty_like(query)
 
 
+@register_ops.register_mindie_fake_op("rf_sparse_attention")
+def _rf_sparse_attention_fake(query, key, value, block_mask, select_idx, select_num_idx, latent_shape, txt_len, scale,
+                              input_layout, inputs_permuted=False):
+    return query.new_empty(query.shape)
+
+
 @register_ops.register_mindie_fake_op("attention_varlen_fwd")
 def _attention_varlen_fwd_fake(query, key, value, cu_seqlens_q, cu_seqlens_k, scale, causal=False):
     return query.new_empty(query.shape)

@@ -6,7 +6,7 @@ import torch
 
 from .sparse_flash_attn_ada_bsa import ada_block_sparse_attention, get_estimate_mask
 from .sparse_flash_attn_rf_v2 import rain_fusion_attention
-from .sparse_flash_attn_rf_v3 import bsa_sparse_attention_v3, do_tensor_rearrange_only
+from .sparse_flash_attn_rf_v3 import bsa_sparse_attention_v3, do_tensor_rearrange_only, permuted_block_sparse_attention
 from ...utils.exception import ParametersInvalid
 from ...utils.status import checked
 
@@ -35,6 +35,11 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attn_mas
         # Compacted block lists straight from the un-permuted q and k.
         _, select_idx, select_num_idx = torch.ops.mindiesd.rf_block_mask(
             q, k, grid, int(txt_len), float(sparsity), float(scale), int(block_size), input_layout, True, -1, True)
+        if q.dtype in (torch.bfloat16, torch.float16) and k.shape == q.shape and block_size == 128:
+            out = permuted_block_sparse_attention(q, k, v, grid, txt_len, scale, input_layout, select_idx=select_idx,
+                                                  select_num_idx=select_num_idx,
+                                                  fuse_loads=bool(kwargs.get("fuse_loads", False)))
+            return checked(out, "sparse_attention")
         q_rf, k_rf, v_rf = do_tensor_rearrange_only(q, k, v, txt_len, latent_shape_q, latent_shape_k, input_layout)
         if input_layout == "BSND":
             q_seq, kv_seq = q_rf.shape[1], k_rf.shape[1]
@@ -54,7 +59,7 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attn_mas
         out, _ = bsa_sparse_attention_v3(q, k, v, latent_shape_q=latent_shape_q, latent_shape_k=latent_shape_k,
                                          txt_len=txt_len, pool_size=block_size, sparsity=sparsity,
                                          input_layout=input_layout, head_num=head_num, scale=scale,
-                                         inner_precise=inner_precise)
+                                         inner_precise=inner_precise, fuse_loads=bool(kwargs.get("fuse_loads", False)))
     elif sparse_type == "ada_bsa":
         smask, sct = get_estimate_mask(q, k, v, scale=scale, head_num=head_num, is_causal=is_causal,
                                        input_layout=input_layout, keep_sink=keep_sink, keep_recent=keep_recent,

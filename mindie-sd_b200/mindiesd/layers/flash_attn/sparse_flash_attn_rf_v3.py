@@ -17,6 +17,30 @@ def do_tensor_rearrange_only(q, k, v, txt_len, latent_shape_q, latent_shape_k, i
     return tuple(torch.ops.mindiesd.rf_rearrange(x, grid, int(txt_len), input_layout, False) for x in (q, k, v))
 
 
+def permutation_fuses(latent_shape, txt_len, dtype) -> bool:
+    """Whether the attention kernel can fetch the window order from un-permuted q, k, v (eight consecutive
+    positions of the permuted order are then eight consecutive tokens of the original one): the grid width
+    and the text length are multiples of 8 and the operands are two-byte floats."""
+    return latent_shape[2] % 8 == 0 and int(txt_len) % 8 == 0 and dtype in (torch.bfloat16, torch.float16)
+
+
+def permuted_block_sparse_attention(q, k, v, grid, txt_len, scale, input_layout, mask=None, select_idx=None,
+                                    select_num_idx=None, fuse_loads=False):
+    """Block-sparse attention in the window order of `grid` on q, k, v given in their ORIGINAL order; the
+    result is in the original order too.  The kernel's epilogue writes every output row straight to its
+    original position, so the inverse permutation of the reference's pipeline costs nothing.  q, k and v
+    are permuted by one gather each -- or, with fuse_loads (and a grid `permutation_fuses` accepts), fetched
+    in window order by the kernel's own loads, which saves the three gathers but makes every 128-token tile
+    32 small copies instead of 2 large ones: at the 21x45x80 grid that is slower, hence off by default."""
+    grid = list(grid)
+    if fuse_loads and permutation_fuses(grid, txt_len, q.dtype) and k.shape == q.shape:
+        return torch.ops.mindiesd.rf_sparse_attention(q, k, v, mask, select_idx, select_num_idx, grid, int(txt_len),
+                                                      float(scale), input_layout, False)
+    q_, k_, v_ = (torch.ops.mindiesd.rf_rearrange(x, grid, int(txt_len), input_layout, False) for x in (q, k, v))
+    return torch.ops.mindiesd.rf_sparse_attention(q_, k_, v_, mask, select_idx, select_num_idx, grid, int(txt_len),
+                                                  float(scale), input_layout, True)
+
+
 def rain_fusion_attention_v3(query, key, value, block_sparse_mask, scale=None, head_num=None,
                              num_key_value_heads=None, input_layout="BNSD", actual_seq_lengths=None,
                              actual_seq_lengths_kv=None, sparse_size=128, inner_precise=4):
@@ -41,7 +65,8 @@ def rain_fusion_attention_v3(query, key, value, block_sparse_mask, scale=None, h
 
 def bsa_sparse_attention_v3(q, k, v, latent_shape_q, latent_shape_k=None, txt_len=0, pool_size=128, sparsity=0.5,
                             input_layout="BSND", head_num=None, num_key_value_heads=None, scale=None,
-                            inner_precise=4, cached_mask=None, protect_first_frame=True, temporal_band=-1):
+                            inner_precise=4, cached_mask=None, protect_first_frame=True, temporal_band=-1,
+                            fuse_loads=False):
     """rearrange -> mask -> block-sparse attention -> inverse rearrange.  Returns (out, mask); pass
     the mask back as `cached_mask` on later steps to skip the mask builder.  `temporal_band` >= 0
     additionally keeps block pairs whose frames lie within that distance (not in the reference)."""
@@ -59,6 +84,10 @@ def bsa_sparse_attention_v3(q, k, v, latent_shape_q, latent_shape_k=None, txt_le
             bool(protect_first_frame), int(temporal_band), False)
     else:
         new_mask = cached_mask
+    if q.dtype in (torch.bfloat16, torch.float16) and k.shape == q.shape and pool_size == 128:
+        out = permuted_block_sparse_attention(q, k, v, grid, txt_len, scale, input_layout, mask=new_mask,
+                                              fuse_loads=fuse_loads)
+        return out, new_mask
     q_, k_, v_ = do_tensor_rearrange_only(q, k, v, txt_len, latent_shape_q, latent_shape_k, input_layout)
     s_dim = 2 if input_layout == "BNSD" else 1
     lens = [q_.shape[s_dim]] * q_.shape[0]

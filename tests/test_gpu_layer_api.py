@@ -60,6 +60,25 @@ def test_la_operator():
         torch.ops.mindiesd.la(q.cuda()[0], k.cuda()[0], v.cuda()[0])
 
 
+@pytest.mark.parametrize("d,dtype", [(64, torch.float16), (88, torch.float16), (40, torch.bfloat16), (96, torch.bfloat16)])
+def test_head_dims_of_the_reference_shape_list(d, dtype):
+    """Head dims 40, 64, 88 and 96 (the reference's shape list, tests/plugin/test_la.csv:2-13, at reduced
+    sequence length and head count) through `la` and `attention_forward`: zero channels are appended up to
+    the kernel's 128 and cut off again."""
+    from mindiesd import attention_forward
+    from mindiesd.layers import _custom_ops as ops
+    q, k, v = (inputs.randn(140 + i, 2, 3, 530, d, dtype=dtype) for i in range(3))
+    want = oa.attention_math(q.float(), k.float(), v.float(), scale=d ** -0.5, head_first=True)
+    lse, out = ops.laser_attention(q.cuda(), k.cuda(), v.cuda(), scale_value=d ** -0.5, head_num=3)
+    assert out.shape == q.shape and out.dtype == torch.float32 and lse.shape == (2, 3, 530)
+    _close(out, want, 1e-2, 1e-3)
+    out2 = attention_forward(q.cuda(), k.cuda(), v.cuda(), head_first=True)  # default scale 1 / sqrt(d)
+    assert out2.shape == q.shape and out2.dtype == dtype
+    _close(out2, want, 2e-2, 2e-3)
+    out3 = attention_forward(*(x.transpose(1, 2).contiguous().cuda() for x in (q, k, v)))
+    _close(out3.transpose(1, 2), want, 2e-2, 2e-3)
+
+
 def _sparse_reference(q, k, v, grid, txt, sparsity, layout):
     """The reference pipeline on CPU with oracle pieces: permute, pool, mask, block-sparse attention,
     inverse permute.  BNSD fp32 result in the caller's token order."""

@@ -135,6 +135,57 @@ def test_block_sparse_mask_and_list_agree_with_oracle(head_first):
     assert _cabi.device_status() == 0
 
 
+@pytest.mark.parametrize("grid,txt,head_first", [
+    ((3, 40, 80), 0, True),      # aligned: every frame in 8x8 windows
+    ((2, 21, 32), 0, True),      # five remainder rows per frame; the first frame stays in raster order
+    ((3, 40, 80), 256, False),   # text tokens move from the front to the back; BSND
+    ((3, 13, 24), 0, True),      # 5 remainder rows, 312 tokens per frame: blocks straddle frames and windows
+])
+def test_permutation_inside_the_attention_kernel(grid, txt, head_first):
+    """The window permutation applied by the attention kernel's own loads and stores against the
+    materialised pipeline (permute q, k, v; attention; inverse permute): the kernel sees the same rows in
+    the same tile order either way, so the outputs are bit-equal."""
+    from mindiesd import _cabi
+    n, s = 2, txt + grid[0] * grid[1] * grid[2]
+    shape = (1, n, s, 128) if head_first else (1, s, n, 128)
+    q, k, v = (inputs.randn(85 + i, *shape, dtype=torch.bfloat16).cuda() for i in range(3))
+    nb = (grid[0] * grid[1] * grid[2] + 127) // 128 + (txt + 127) // 128
+    assert nb == (s + 127) // 128  # image and text blocks coincide with blocks of the whole sequence here
+    m = np.random.RandomState(11).rand(1, n, nb, nb) < 0.4
+    m[:, :, np.arange(nb), np.arange(nb)] = True
+    mask = torch.from_numpy(m.astype(np.int8)).cuda()
+    qp, kp, vp = (_cabi.rf_rearrange(x, grid, txt, head_first) for x in (q, k, v))
+    want = _cabi.rf_rearrange(_cabi.attention(qp, kp, vp, head_first=head_first, block_mask=mask), grid, txt, head_first,
+                              inverse=True)
+    got = _cabi.attention(q, k, v, head_first=head_first, block_mask=mask, perm_grid=grid, perm_txt=txt)
+    assert torch.equal(got, want)
+    # inputs permuted beforehand, only the output put back by the kernel (what the layer API does)
+    got1 = _cabi.attention(qp, kp, vp, head_first=head_first, block_mask=mask, perm_grid=grid, perm_txt=txt,
+                           perm_inputs_permuted=True)
+    assert torch.equal(got1, want)
+    sel, num = orf.select_lists(mask.cpu())
+    got2 = _cabi.attention(q, k, v, head_first=head_first, select_idx=sel.cuda(), select_num=num.cuda(), perm_grid=grid,
+                           perm_txt=txt)
+    assert torch.equal(got2, want)
+    assert _cabi.device_status() == 0
+
+
+def test_permutation_inside_the_kernel_needs_eight_token_runs():
+    from mindiesd import _cabi
+    grid = (3, 30, 52)  # four remainder columns: runs of four tokens
+    s = grid[0] * grid[1] * grid[2]
+    q = torch.zeros(1, 1, s, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(_cabi.NativeLibraryError):
+        _cabi.attention(q, q, q, perm_grid=grid)
+    # ... but putting only the output back works on any grid
+    x = inputs.randn(89, 1, 1, s, 128, dtype=torch.bfloat16).cuda()
+    xp = _cabi.rf_rearrange(x, grid, 0, True)
+    want = _cabi.rf_rearrange(_cabi.attention(xp, xp, xp), grid, 0, True, inverse=True)
+    assert torch.equal(_cabi.attention(xp, xp, xp, perm_grid=grid, perm_inputs_permuted=True), want)
+    with pytest.raises(_cabi.NativeLibraryError):
+        _cabi.attention(q, q, q, perm_grid=(3, 40, 80))  # does not match the sequence length
+
+
 def test_full_mask_equals_dense():
     from mindiesd import _cabi
     q, k, v = (inputs.randn(80 + i, 1, 2, 900, 128, dtype=torch.bfloat16).cuda() for i in range(3))
