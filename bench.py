@@ -238,7 +238,8 @@ def dense_or_ulysses(args, rank, world, device):
             pieces = default_head_pieces(cfg.heads // world, cfg.seq)
         qs, ks, vs = (x[:, rank * s_loc:(rank + 1) * s_loc].contiguous() for x in (q, k, v))
         checked = sorted({0, cfg.heads // 2 + 1, cfg.heads - 1})  # heads of the first, a middle and the last rank
-        ok = ulysses_parity(q, k, v, ulysses_attention(qs, ks, vs, head_chunks=pieces), rank, world, checked)
+        ok = ulysses_parity(q, k, v, ulysses_attention(qs, ks, vs, head_chunks=pieces, transport=args.ulysses_transport),
+                            rank, world, checked)
         flag = torch.tensor([1 if ok else 0], device=device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         parity = {"heads": checked, "equal": bool(flag.item()), "against": "single-GPU kernel on the unsharded tensors, torch.equal, every rank"}
@@ -252,7 +253,7 @@ def dense_or_ulysses(args, rank, world, device):
         out = torch.empty_like(q)
         layer = lambda: _cabi.attention(q, k, v, head_first=False, out=out)  # noqa: E731
     else:
-        layer = lambda: ulysses_attention(q, k, v, head_chunks=pieces)  # noqa: E731
+        layer = lambda: ulysses_attention(q, k, v, head_chunks=pieces, transport=args.ulysses_transport)  # noqa: E731
 
     # The timed region should last about two seconds at every GPU count, so that every N runs in the
     # same power state (a short region finishes before the power cap engages): a step repeats the
@@ -282,7 +283,7 @@ def dense_or_ulysses(args, rank, world, device):
     phases = None
     if world > 1:  # one more, untimed, call with CUDA events around each phase
         prof = {}
-        ulysses_attention(q, k, v, head_chunks=pieces, profile=prof)
+        ulysses_attention(q, k, v, head_chunks=pieces, profile=prof, transport=args.ulysses_transport)
         t = torch.tensor([prof.get(n, 0.0) for n in ("pack", "exchange_in", "attention", "exchange_out", "unpack")],
                          dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -325,7 +326,8 @@ def dense_or_ulysses(args, rank, world, device):
     value = cfg.flops / (ms_layer * 1e-3) / 1e12
     config = {"workload": WORKLOAD if not args.heads else WORKLOAD.replace("N40", f"N{cfg.heads}") + " [heads reduced]",
               "layout": "BSND",
-              "parallelism": "single GPU" if world == 1 else f"ulysses sp{world}, local heads in pieces of {pieces}",
+              "parallelism": "single GPU" if world == 1 else
+              f"ulysses sp{world}, local heads in pieces of {pieces}, exchange over {args.ulysses_transport or 'nccl'}",
               "layers_per_step": layers, "ms_per_layer": ms_layer, "flops_per_layer": cfg.flops,
               "l2": "operands (3.1 GB per layer) exceed L2; no flush",
               "tflops_per_gpu": value / world, "kernel_status": status}
@@ -533,6 +535,8 @@ def main():
     ap.add_argument("--sparsity", type=float, default=0.75)
     ap.add_argument("--band", type=int, default=-1)
     ap.add_argument("--ulysses-chunks", type=int, default=0, help="head chunks per rank of the Ulysses leg (0: the API's default)")
+    ap.add_argument("--ulysses-transport", default=None, choices=[None, "nccl", "peer"],
+                    help="how the Ulysses leg exchanges data (default: the API's)")
     ap.add_argument("--e2e-chunks", type=int, default=0, help="head chunks of the pipelined end-to-end leg (0: the API's default)")
     ap.add_argument("--cdf", type=float, default=0.9, help="cumulative-mass threshold of the ada_bsa estimate")
     ap.add_argument("--heads", type=int, default=0, help="reduced head count for profiler captures (default: the full 40)")

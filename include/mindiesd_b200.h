@@ -449,6 +449,20 @@ typedef struct mindiesd_ulysses_move_args {
 int mindiesd_ulysses_move(const mindiesd_ulysses_move_args* args, void* stream);
 
 /*
+ * Peer memory for the sequence-parallel exchange (one process per GPU on one box).  mindiesd_peer_export
+ * turns a device pointer of this process into a 64-byte handle plus the pointer's offset inside its
+ * allocation; the other rank passes both to mindiesd_peer_open (with ITS device current) and gets an
+ * address it may hand to mindiesd_ulysses_move as a table entry: stores to it and loads from it cross
+ * NVLink.  An allocation is mapped once per process and stays mapped until the process exits; the
+ * exporting rank must keep the allocation alive as long as any peer uses it.  Positive return values are
+ * cudaError_t codes (e.g. no peer access between the two devices).
+ * The reference has no counterpart: its documented Ulysses pattern moves everything through the
+ * collective library (docs/zh/features/parallelism.md:207-233).
+ */
+int mindiesd_peer_export(const void* ptr, uint8_t handle[64], uint64_t* offset);
+int mindiesd_peer_open(const uint8_t handle[64], uint64_t offset, void** ptr);
+
+/*
  * Strided copy between pinned host memory and device memory (either direction, chosen by the
  * addresses) on a stream: `height` rows of `width_bytes`, rows `*_pitch` bytes apart.  It lets a
  * host-resident [rows, N, D] tensor be brought in one head range at a time, so that the first piece

@@ -63,16 +63,22 @@ constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) compiles to:
 //   1  the same in two halves of 64 keys
 //   2  block max first; P stored chunk by chunk as it is computed and handed over after 96 and 128
 //      keys; the row sum is taken after the hand-over, off the path the MMA thread waits on
+#ifndef SDB_FA_RESPLIT
+#define SDB_FA_RESPLIT 1
+#endif
 #ifndef SDB_FA_RESPLIT_FP8
 #define SDB_FA_RESPLIT_FP8 0
 #endif
 // Of the eight groups of four scores in a 32-column chunk, how many take the exponentials of their
 // second pair on the FMA pipe (ex2_poly2) instead of the exponent unit: 8 = half of all exponentials.
+// Measured at the benchmark shape: the e4m3 kernel, whose softmax loop is bound by the exponent unit,
+// gains 7 % with a quarter of its exponentials moved (4) and loses with half (8); the two-byte kernels,
+// bound by instruction issue and latency in that loop, lose with any (4: -2 %, 8: -12 %).
 #ifndef SDB_FA_POLY
 #define SDB_FA_POLY 0
 #endif
 #ifndef SDB_FA_POLY_FP8
-#define SDB_FA_POLY_FP8 SDB_FA_POLY
+#define SDB_FA_POLY_FP8 4
 #endif
 #ifndef SDB_FA_DEFER_SUM_FP8
 #define SDB_FA_DEFER_SUM_FP8 0
@@ -157,7 +163,7 @@ __device__ __forceinline__ void poison_row(const FaParams& p, int batch, int hea
 template <int kIn>
 __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_constant__ FaParams p) {
     constexpr bool kFp8 = kIn == 3;
-    constexpr bool kResplit = SDB_FA_RESPLIT_FP8 || !kFp8;  // whether the warpgroups re-split their registers
+    constexpr bool kResplit = (SDB_FA_RESPLIT_FP8 || !kFp8) && SDB_FA_RESPLIT;  // whether the warpgroups re-split their registers
     constexpr bool kSplit = kFp8 || kHalves || kMaxFirst;  // P is handed to the MMA thread in two parts
     // 32-key chunks of a block in the first part: half of the block, or three quarters when the
     // exponentials of a two-byte block are taken max-first (the second part's product is then short).
@@ -902,6 +908,10 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             int out_row = q_row;
             if (p.perm_on && row_ok) out_row = source_of(make_grid(p.perm_t, p.perm_h, p.perm_w, p.perm_txt), q_row);
             // l_run carries the 2^8 shift of the stored e4m3 probabilities, so it cancels in O / l.
+            // A row that sees no key at all (causal, more queries than keys) gives zeros whatever its
+            // masked scores were turned into.
+            const bool sees_keys = !p.causal || q_row + causal_off >= 0;
+            if (!sees_keys) l_run = 0.0f;
             const float inv_l = l_run > 0.0f ? v_ref / l_run : 0.0f;
             const float* v_ch = (kFp8 && p.v_scale_block == 0)
                                     ? p.v_scale + (static_cast<int64_t>(batch) * p.kv_heads + kv_head) * kHeadDim
@@ -991,7 +1001,7 @@ static cudaError_t launch_one(const FaParams& p, cudaStream_t stream) {
         cudaFuncAttributes attr;
         return cudaFuncGetAttributes(&attr, fa_fwd_kernel<kIn>) == cudaSuccess ? attr.numRegs : 0;
     }();
-    if ((SDB_FA_RESPLIT_FP8 || kIn != 3) && 2 * 128 * kRegsSoftmax + 128 * kRegsOther > kThreads * launch_regs)
+    if (SDB_FA_RESPLIT && (SDB_FA_RESPLIT_FP8 || kIn != 3) && 2 * 128 * kRegsSoftmax + 128 * kRegsOther > kThreads * launch_regs)
         return cudaErrorLaunchOutOfResources;
     // Packed sequences: every sequence rounds its tile pairs up, so seq_q / 256 + num_seqs bounds their number.
     const int pairs = p.cu_seqlens_q ? p.seq_q / (2 * kTile) + p.num_seqs : (p.seq_q + 2 * kTile - 1) / (2 * kTile);

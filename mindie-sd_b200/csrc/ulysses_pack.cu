@@ -138,6 +138,9 @@ __global__ void __launch_bounds__(256) ulysses_move_kernel(const MoveParams p) {
             }
         }
     }
+    // The destinations may be another GPU's memory: make this thread's stores visible system-wide before
+    // the kernel counts as complete, so that whatever orders the ranks afterwards also orders the data.
+    __threadfence_system();
 }
 
 struct RopeParams {

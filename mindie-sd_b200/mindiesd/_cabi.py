@@ -490,3 +490,23 @@ def copy_2d(dst_ptr, dst_pitch, src_ptr, src_pitch, width_bytes, height, stream)
     fn.restype = C.c_int
     fn.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p]
     check(fn(dst_ptr, dst_pitch, src_ptr, src_pitch, width_bytes, height, stream.cuda_stream), "mindiesd_copy_2d")
+
+
+def peer_export(t: torch.Tensor):
+    """(handle bytes, offset) that lets another process on this box map tensor `t` (mindiesd_peer_export)."""
+    fn = lib().mindiesd_peer_export
+    fn.restype, fn.argtypes = C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint64)]
+    handle = (C.c_uint8 * 64)()
+    offset = C.c_uint64(0)
+    check(fn(t.data_ptr(), handle, C.byref(offset)), "mindiesd_peer_export")
+    return bytes(handle), int(offset.value)
+
+
+def peer_open(handle: bytes, offset: int) -> int:
+    """Device address, valid on the current device, of the buffer another process exported."""
+    fn = lib().mindiesd_peer_open
+    fn.restype, fn.argtypes = C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p)]
+    buf = (C.c_uint8 * 64).from_buffer_copy(handle)
+    ptr = C.c_void_p(0)
+    check(fn(buf, offset, C.byref(ptr)), "mindiesd_peer_open")
+    return int(ptr.value)

@@ -15,6 +15,12 @@ this is the same tensor contract -- BSND in, BSND out, `N % world_size == 0` -- 
   c's attention.  Pieces may be uneven (5 local heads -> 2 + 3), so that overlap exists at every
   world size.
 * Send and receive buffers are allocated once per (shape, dtype, group) and reused by every call.
+* transport="peer": the ranks map each other's receive buffers (CUDA IPC) once, and then the re-shard
+  kernel IS the all-to-all: it stores each destination's block straight into that rank's receive
+  buffer over NVLink, and after attention every rank's scatter kernel loads the blocks it needs straight
+  from its peers' output buffers.  No send buffers, no NCCL data movement: the only collective left is a
+  one-element all-reduce per piece that orders the ranks.  transport="nccl" (the default where the
+  mapping is not available) packs into a send buffer and calls all_to_all_single.
 """
 from __future__ import annotations
 
@@ -63,6 +69,39 @@ def _buffers(key, shapes, dtype, device):
 def release_buffers():
     """Frees the persistent exchange buffers (they are re-created by the next call)."""
     _BUFFERS.clear()
+    _PEER_BUFFERS.clear()
+
+
+_PEER_BUFFERS = {}
+
+
+class _PeerBuffers:
+    """Receive and output buffers of one call signature, mapped into every rank of the group.
+    local[i] is this rank's buffer i; peer_ptr[r][i] the address, in THIS process, of the same buffer of
+    rank r (for r == rank the local one).  The mapping goes through CUDA IPC handles exchanged once."""
+
+    def __init__(self, shapes, dtype, device, group):
+        from .. import _cabi
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        self.local = [torch.empty(s, dtype=dtype, device=device) for s in shapes]
+        handles = [_cabi.peer_export(t) for t in self.local]
+        gathered = [None] * world
+        dist.all_gather_object(gathered, handles, group=group)
+        with torch.cuda.device(device):
+            self.peer_ptr = [[t.data_ptr() for t in self.local] if r == rank else
+                             [_cabi.peer_open(h, off) for h, off in gathered[r]] for r in range(world)]
+        self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        dist.barrier(group=group)  # nobody proceeds (or frees) before everyone has mapped
+
+
+def _peer_buffers(key, shapes, dtype, device, group):
+    cached = _PEER_BUFFERS.get(key)
+    if cached is None:
+        if len(_PEER_BUFFERS) >= 4:
+            _PEER_BUFFERS.pop(next(iter(_PEER_BUFFERS)))
+        cached = _PeerBuffers(shapes, dtype, device, group)
+        _PEER_BUFFERS[key] = cached
+    return cached
 
 
 def default_head_pieces(local_heads: int, seq: int = 1 << 30, batch: int = 1, limit: int = 8):
@@ -170,7 +209,7 @@ def _move(tensors, table, rows, world, n_loc, head0, heads, inverse=False, rope=
 def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, group=None,
                       scale: Optional[float] = None, head_chunks: Union[None, int, Sequence[int]] = None,
                       attn_fn: Optional[Callable] = None, rope=None, profile: Optional[dict] = None,
-                      _piece_ready: Optional[Callable] = None, _piece_done: Optional[Callable] = None,
+                      transport: Optional[str] = None, _piece_ready: Optional[Callable] = None, _piece_done: Optional[Callable] = None,
                       _out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """query/key/value: this rank's [B, S/P, N, D] slice (BSND).  Returns this rank's [B, S/P, N, D]
     slice of the attention output over the full sequence.
@@ -182,6 +221,9 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
     rope: (cos, sin, rotated_mode) -- fp32 tables [S/P, D] for this rank's tokens and "rotated_half" or
     "rotated_interleaved": q and k are rotated as `rotary_position_embedding` would, inside the kernel that
     re-shards them, so the rotated tensors are never written on this rank.
+    transport: "nccl" (pack, all_to_all_single, unpack), "peer" (the re-shard kernels store to and load from
+    the peers' buffers over NVLink; CUDA tensors, B = 1, default attention), or None: the environment variable
+    MINDIESD_ULYSSES_TRANSPORT, else "nccl".
     profile: a dict that receives the summed CUDA-event milliseconds of the phases of this call
     ("pack", "exchange_in", "attention", "exchange_out", "unpack"); it synchronises the device.
     """
@@ -218,11 +260,20 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
     out = _out if _out is not None else torch.empty_like(q)
     outr = out.view(rows, n, d)
 
+    import os
+    transport = transport or os.environ.get("MINDIESD_ULYSSES_TRANSPORT", "nccl")
+    if transport not in ("nccl", "peer"):
+        raise ParametersInvalid(f"transport must be 'nccl' or 'peer', but got {transport}.")
+    if transport == "peer" and not (cuda and b == 1 and attn_fn is None):
+        raise ParametersInvalid("transport='peer' needs CUDA tensors, batch 1 and the default attention.")
+    key_ = (device, q.dtype, world, b, s_loc, n, d, tuple(sizes), id(group))
+    if transport == "peer":
+        return _ulysses_peer(qr, kr, vr, out, outr, sizes, world, dist.get_rank(group), rows, n_loc, d, scale, group,
+                             rope_args, profile, key_, _piece_ready, _piece_done)
     # One set of buffers per piece: a piece's buffers are free again when the call returns.
     shapes = []
     for h in sizes:
         shapes += [(world, rows, 3 * h, d)] * 2 + [(world, rows, h, d)] * 2  # send, recv, o_send, o_recv
-    key_ = (device, q.dtype, world, b, s_loc, n, d, tuple(sizes), id(group))
     bufs = _buffers(key_, shapes, q.dtype, device)
 
     compute = comm = None
@@ -309,6 +360,75 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
         # compute stream has waited for; the buffers are only touched again by the next call, which
         # orders itself behind this one on both streams.
         comm.wait_stream(compute)
+    timer.finish()
+    return out
+
+
+def _ulysses_peer(qr, kr, vr, out, outr, sizes, world, rank, rows, n_loc, d, scale, group, rope_args, profile, key_,
+                  piece_ready, piece_done):
+    """The exchange over peer memory.  Per piece c (communication stream): the re-shard kernel writes, for
+    every rank r, that rank's heads of my rows into rows [rank * rows, ...) of r's receive buffer c; a
+    one-element all-reduce then tells every rank that all blocks of piece c have been written.  Compute
+    stream: attention on my receive buffer into my output buffer c; another one-element all-reduce; then
+    the scatter kernel loads, from every rank r, the rows of r's output buffer c that are mine."""
+    from .. import _cabi
+    device = qr.device
+    shapes = []
+    for h in sizes:
+        shapes += [(world * rows, 3 * h, d), (world * rows, h, d)]  # receive buffer [S, 3h, D], output buffer [S, h, D]
+    pb = _peer_buffers(key_ + ("peer",), shapes, qr.dtype, device, group)
+    compute = torch.cuda.current_stream(device)
+    comm = _comm_stream(device)
+    comm.wait_stream(compute)
+    timer = _Timer(profile, True)
+    esz = qr.element_size()
+    head0 = [sum(sizes[:c]) for c in range(len(sizes))]
+
+    def order_ranks(stream_name):
+        # Every rank reaches this point of its stream before any rank leaves it.
+        dist.all_reduce(pb.flag, group=group)
+
+    def send(c):
+        h = sizes[c]
+        with torch.cuda.stream(comm):
+            if piece_ready is not None:
+                piece_ready(c, head0[c], h, comm)
+            with timer.span("pack", comm):
+                ptrs = [pb.peer_ptr[r][2 * c] + rank * rows * 3 * h * d * esz for r in range(world)]
+                cos = sin = None
+                mode = 0
+                if rope_args is not None:
+                    cos, sin, mode = rope_args
+                _cabi.ulysses_move((qr, kr, vr), ptrs, 3 * h * d, rows, world, n_loc, head0[c], h, cos=cos, sin=sin,
+                                   rope_mode=mode, thread_blocks=0 if c == 0 else 32)
+            with timer.span("exchange_in", comm):
+                order_ranks("comm")
+            ev = torch.cuda.Event()
+            ev.record(comm)
+            return ev
+
+    arrived = send(0)
+    for c, h in enumerate(sizes):
+        ready = arrived
+        if c + 1 < len(sizes):
+            arrived = send(c + 1)
+        compute.wait_event(ready)
+        recv, o_buf = pb.local[2 * c], pb.local[2 * c + 1]
+        full = recv.view(1, world * rows, 3 * h, d)
+        with timer.span("attention", compute):
+            _cabi.attention(full[:, :, 0:h], full[:, :, h:2 * h], full[:, :, 2 * h:3 * h], head_first=False, scale=scale,
+                            out=o_buf.view(1, world * rows, h, d))
+        with timer.span("exchange_out", compute):
+            order_ranks("compute")
+        with timer.span("unpack", compute):
+            ptrs = [pb.peer_ptr[r][2 * c + 1] + rank * rows * h * d * esz for r in range(world)]
+            _cabi.ulysses_move((outr,), ptrs, h * d, rows, world, n_loc, head0[c], h, inverse=True)
+        if piece_done is not None:
+            piece_done(c, head0[c], h, compute)
+    # The next call writes into the peers' receive buffers and this rank's output buffers again: it may only
+    # start once every rank has finished reading them, i.e. after everyone's last scatter kernel.
+    order_ranks("compute")
+    comm.wait_stream(compute)
     timer.finish()
     return out
 

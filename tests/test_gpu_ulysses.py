@@ -54,6 +54,16 @@ def _worker(rank, world, port, head_chunks, result):
         for rep in range(2):
             ho = ulysses_attention_host(hq, hk, hv, head_chunks=head_chunks)
             checks[f"host{rep}"] = torch.equal(ho, shard(want).cpu())
+        # the exchange over peer memory: the re-shard kernels store to / load from the other ranks' buffers
+        for rep in range(2):
+            out_p = ulysses_attention(shard(q), shard(k), shard(v), head_chunks=head_chunks, transport="peer")
+            torch.cuda.synchronize()
+            checks[f"peer{rep}"] = torch.equal(out_p, shard(want))
+        cs, ss = (x.chunk(world, dim=0)[rank].contiguous() for x in (cos, sin))
+        qr, kr = (rotary_position_embedding(x, cos, sin, "rotated_half", head_first=False) for x in (q, k))
+        out_pr = ulysses_attention(shard(q), shard(k), shard(v), head_chunks=head_chunks, transport="peer",
+                                   rope=(cs, ss, "rotated_half"))
+        checks["peer_rope"] = torch.equal(out_pr, shard(_cabi.attention(qr, kr, v, head_first=False)))
         prof = {}
         ulysses_attention(shard(q), shard(k), shard(v), head_chunks=head_chunks, profile=prof)
         checks["profile"] = set(prof) == {"pack", "exchange_in", "attention", "exchange_out", "unpack"}
