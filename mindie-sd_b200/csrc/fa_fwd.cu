@@ -47,10 +47,20 @@ constexpr int kMmaWarp = 8;
 constexpr int kLoadWarp = 9;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
-// Register budgets after the roles split.  The registers a warpgroup may take are the ones another
-// warpgroup of the SAME thread block gave back: the pool is what the launch gave the block (threads x
-// registers per thread as compiled, 384 x 168), not the SM's register file.  A request beyond it never
-// returns -- there is no time limit on that wait -- so the sum is checked here.
+// ---- build-time choices, each measured at the benchmark shape (B1 N40 S75600, bf16 unless noted) ----------
+//
+// Register re-split between the warpgroups after the roles part (setmaxnreg).  The registers a warpgroup
+// may take are the ones another warpgroup of the SAME thread block gave back: the pool is what the launch
+// gave the block (threads x registers per thread as compiled, 384 x 168), not the SM's register file.  A
+// request beyond it never returns -- there is no time limit on that wait -- so the sum is checked below and
+// again at launch.  Measured: no difference (103.3-103.9 ms without, 104.0-105.0 ms with 216 / 72), so the
+// plain launch allocation is built.
+#ifndef SDB_FA_RESPLIT
+#define SDB_FA_RESPLIT 0
+#endif
+#ifndef SDB_FA_RESPLIT_FP8
+#define SDB_FA_RESPLIT_FP8 0
+#endif
 #ifndef SDB_FA_REGS_SOFTMAX
 #define SDB_FA_REGS_SOFTMAX 216
 #endif
@@ -58,36 +68,31 @@ constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
 #define SDB_FA_REGS_OTHER 72
 #endif
 constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) compiles to: 65536 / 384 rounded down to 8
-// How the softmax warps treat a block of two-byte operands (e4m3 always uses the last form):
+// How the softmax warps treat a block of two-byte operands (e4m3 always uses the second form):
 //   0  exponentials against the running max right away, overflow caught by a row-sum test, P handed over whole
-//   1  the same in two halves of 64 keys
 //   2  block max first; P stored chunk by chunk as it is computed and handed over after 96 and 128
 //      keys; the row sum is taken after the hand-over, off the path the MMA thread waits on
-#ifndef SDB_FA_RESPLIT
-#define SDB_FA_RESPLIT 1
-#endif
-#ifndef SDB_FA_RESPLIT_FP8
-#define SDB_FA_RESPLIT_FP8 0
+// Both pass the same tests and measure the same (105.7 ms each on one GPU); 0 is built.
+#ifndef SDB_FA_BF16_MODE
+#define SDB_FA_BF16_MODE 0
 #endif
 // Of the eight groups of four scores in a 32-column chunk, how many take the exponentials of their
 // second pair on the FMA pipe (ex2_poly2) instead of the exponent unit: 8 = half of all exponentials.
-// Measured at the benchmark shape: the e4m3 kernel, whose softmax loop is bound by the exponent unit,
-// gains 7 % with a quarter of its exponentials moved (4) and loses with half (8); the two-byte kernels,
-// bound by instruction issue and latency in that loop, lose with any (4: -2 %, 8: -12 %).
+// Measured: the e4m3 kernel, whose softmax loop is bound by the exponent unit, gains with a quarter of its
+// exponentials moved (86.5 ms against 92.8 ms) and loses with half; the two-byte kernels, bound by
+// instruction issue and latency in that loop, lose with any (a quarter: -2 %, half: -12 %).
 #ifndef SDB_FA_POLY
 #define SDB_FA_POLY 0
 #endif
 #ifndef SDB_FA_POLY_FP8
 #define SDB_FA_POLY_FP8 4
 #endif
+// e4m3 sums its probabilities as it goes (1: after the hand-over, like the two-byte max-first form).
 #ifndef SDB_FA_DEFER_SUM_FP8
 #define SDB_FA_DEFER_SUM_FP8 0
 #endif
-#ifndef SDB_FA_BF16_MODE
-#define SDB_FA_BF16_MODE 0
-#endif
 constexpr int kBf16Mode = SDB_FA_BF16_MODE;
-constexpr bool kHalves = kBf16Mode == 1;
+static_assert(kBf16Mode == 0 || kBf16Mode == 2, "SDB_FA_BF16_MODE");
 constexpr bool kMaxFirst = kBf16Mode == 2;
 constexpr int kRegsSoftmax = SDB_FA_REGS_SOFTMAX;
 constexpr int kRegsOther = SDB_FA_REGS_OTHER;
@@ -164,7 +169,7 @@ template <int kIn>
 __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_constant__ FaParams p) {
     constexpr bool kFp8 = kIn == 3;
     constexpr bool kResplit = (SDB_FA_RESPLIT_FP8 || !kFp8) && SDB_FA_RESPLIT;  // whether the warpgroups re-split their registers
-    constexpr bool kSplit = kFp8 || kHalves || kMaxFirst;  // P is handed to the MMA thread in two parts
+    constexpr bool kSplit = kFp8 || kMaxFirst;  // P is handed to the MMA thread in two parts
     // 32-key chunks of a block in the first part: half of the block, or three quarters when the
     // exponentials of a two-byte block are taken max-first (the second part's product is then short).
     constexpr int kFirstChunks = (!kFp8 && kMaxFirst) ? 3 : 2;
@@ -188,10 +193,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     // operands hand a block over whole, on the second barrier.
     auto bar_p = [&](int t, int h) { return bar_base + 8u * (3 + 2 * C::kStages + 2 * t + h); };
     auto bar_done = [&]() { return bar_base + 8u * (7 + 2 * C::kStages); };
-    // First half of a tile's P V product complete (two-byte operands handing P over in halves): only
-    // waited for on the rare path that must rescale O between the halves.
-    auto bar_h = [&](int t) { return bar_base + 8u * (8 + 2 * C::kStages + t); };
-    constexpr int kNumBars = 10 + 2 * C::kStages;
+    constexpr int kNumBars = 8 + 2 * C::kStages;
     static_assert(kNumBars * 8 + 16 <= 256, "barrier area");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -262,8 +264,6 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             mbar_init(bar_p(t, 1), kTile);
         }
         mbar_init(bar_done(), 1);
-        mbar_init(bar_h(0), 1);
-        mbar_init(bar_h(1), 1);
         *abort_flag = 0;
         *abort_site = 0;
         fence_mbar_init();
@@ -485,7 +485,6 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                         SDB_TR(2, u, 1);
                         issue_pv(0, 0, vslot.idx, pv_cnt[0] > 0);
                         SDB_TR(2, u, 2);
-                        if constexpr (kHalves && !kFp8) umma_commit(bar_h(0));
                     }
                     ok = mbar_wait(bar_p(0, 1), static_cast<uint32_t>(pv_cnt[0]) & 1u, abort_flag, 13, wait_us);
                     if (!ok) break;
@@ -511,7 +510,6 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                         SDB_TR(2, u, 6);
                         issue_pv(1, 0, vslot.idx, pv_cnt[1] > 0);
                         SDB_TR(2, u, 7);
-                        if constexpr (kHalves && !kFp8) umma_commit(bar_h(1));
                     }
                     ok = mbar_wait(bar_p(1, 1), static_cast<uint32_t>(pv_cnt[1]) & 1u, abort_flag, 14, wait_us);
                     if (!ok) break;
@@ -658,94 +656,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(mx8[i], __uint_as_float(s[3][i + 24]));
                 return fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             };
-            if constexpr (!kFp8 && kHalves) {
-                // As below, but in two halves of 64 keys, each tested and handed over by itself, so that the
-                // first half of the P V product runs while the second half's exponentials are taken.  If the
-                // SECOND half fails its test, the first is already with the MMA thread: the row waits for
-                // that half product (bar_h), then rescales O -- which holds it -- and redoes its own half.
-                if (cnt == 0) m_run = fmaxf(row_max() * mult, -3.0e38f);
-                const uint64_t mult2 = pack2(mult, mult);
-                auto rescale_o = [&](float alpha) {
-    #pragma unroll 1
-                    for (int c = 0; c < kHeadDim / 8; ++c) {
-                        uint32_t o[8];
-                        tmem_ld8(taddr_o + c * 8, o);
-                        tmem_wait_ld();
-    #pragma unroll
-                        for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st8(taddr_o + c * 8, o);
-                    }
-                };
-                auto half = [&](auto hconst) -> bool {
-                    constexpr int h = decltype(hconst)::value;
-                    uint32_t pk[2][16];
-                    float sum = 0.0f;
-    #pragma unroll 1
-                    for (int pass = 0; pass < 2; ++pass) {
-                        const float neg_m = -m_run;
-                        const uint64_t negm2 = pack2(neg_m, neg_m);
-                        uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
-    #pragma unroll
-                        for (int cc = 0; cc < 2; ++cc) {
-                            constexpr int base = 2 * h;
-    #pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                float e0, e1, e2, e3;
-                                unpack2(fma2(pack2(__uint_as_float(s[base + cc][4 * i]), __uint_as_float(s[base + cc][4 * i + 1])), mult2, negm2), e0, e1);
-                                e0 = ex2_approx(e0);
-                                e1 = ex2_approx(e1);
-                                unpack2(fma2(pack2(__uint_as_float(s[base + cc][4 * i + 2]), __uint_as_float(s[base + cc][4 * i + 3])), mult2, negm2), e2, e3);
-                                e2 = ex2_approx(e2);
-                                e3 = ex2_approx(e3);
-                                sum2[0] = add2(sum2[0], pack2(e0, e1));
-                                sum2[1] = add2(sum2[1], pack2(e2, e3));
-                                pk[cc][2 * i] = pack_pair(e0, e1, kIn);
-                                pk[cc][2 * i + 1] = pack_pair(e2, e3, kIn);
-                            }
-                        }
-                        {
-                            float a, b;
-                            unpack2(add2(sum2[0], sum2[1]), a, b);
-                            sum = a + b;
-                        }
-                        if (pass == 1 || cnt == 0) break;
-                        if (!__any_sync(0xffffffffu, !(sum <= kRedoSum))) break;
-                        if constexpr (h == 1) {
-                            // the first half's product must be over before O changes
-                            if (!__all_sync(0xffffffffu, mbar_wait(bar_h(t), static_cast<uint32_t>(cnt) & 1u, abort_flag, 24 + t, wait_us)))
-                                return false;
-                            tc_fence_after();
-                        }
-                        // Scores not yet stored over: all of them (first half) or keys 64-127 (second half).
-    #pragma unroll
-                        for (int c = 2 * h; c < 4; ++c) tmem_ld32(taddr_s + c * 32, s[c]);
-                        tmem_wait_ld();
-                        if (masked) mask_scores();
-                        float mx = -INFINITY;
-                        if constexpr (h == 0) {
-                            mx = row_max();
-                        } else {
-    #pragma unroll
-                            for (int i = 0; i < 32; ++i) mx = fmax3(mx, __uint_as_float(s[2][i]), __uint_as_float(s[3][i]));
-                        }
-                        const float m_new = fmaxf(m_run, mx * mult);
-                        const float alpha = ex2_approx(m_run - m_new);
-                        m_run = m_new;
-                        l_run *= alpha;
-                        rescale_o(alpha);
-                    }
-    #pragma unroll
-                    for (int cc = 0; cc < 2; ++cc) tmem_st16(taddr_s + (2 * h + cc) * 16, pk[cc]);
-                    l_run += sum;
-                    tmem_wait_st();
-                    tc_fence_before();
-                    mbar_arrive(bar_p(t, h));
-                    return true;
-                };
-                ok = half(std::integral_constant<int, 0>{});
-                if (ok) ok = half(std::integral_constant<int, 1>{});
-                if (!ok) break;
-            } else if constexpr (!kFp8 && !kMaxFirst) {
+            if constexpr (!kFp8 && !kMaxFirst) {
                 // The probabilities are taken against the running max right away and kept in registers; the
                 // scores die as they are consumed.  Every probability is non-negative, so a row sum within
                 // 2^lag bounds each of them: only if that test fails somewhere in the warp -- rare after the

@@ -51,12 +51,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // and short enough that a grid of stuck thread blocks drains at once (the blocks that are resident
 // give up together; the ones that start afterwards see the status word and leave).
 constexpr uint32_t kWaitLimitUs = 1000000u;
-#ifndef SDB_WAIT_MODE
-#define SDB_WAIT_MODE 0
-#endif
-#ifndef SDB_WAIT_SLEEP_NS
-#define SDB_WAIT_SLEEP_NS 64
-#endif
+
 
 // Waits for the phase with the given parity, for at most limit_us microseconds of wall-clock time
 // (the nanosecond timer of the device, which does not depend on the SM clock).  Returns false if
@@ -64,17 +59,14 @@ constexpr uint32_t kWaitLimitUs = 1000000u;
 // first to give up raises the flag and leaves `site` (a small number naming the wait) next to it.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site = 0,
                                           uint32_t limit_us = kWaitLimitUs) {
-    if (mbar_try_wait(bar, parity)) return true;
-#if SDB_WAIT_MODE == 1
+    // Waits inside these kernels end within microseconds: a first phase polls without touching the timer
+    // or the flag, so the common case costs what a bare wait costs.  (Each attempt suspends the thread for a
+    // hardware-chosen while by itself.)
 #pragma unroll 1
-    for (int i = 0; i < 32; ++i)
+    for (int i = 0; i < 1024; ++i)
         if (mbar_try_wait(bar, parity)) return true;
-#endif
     const uint64_t t0 = global_timer_ns();
     for (uint32_t i = 1;; ++i) {
-#if SDB_WAIT_MODE == 2
-        asm volatile("nanosleep.u32 %0;" ::"n"(SDB_WAIT_SLEEP_NS));
-#endif
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63u) == 0u) {
             if (*abort_flag) return false;

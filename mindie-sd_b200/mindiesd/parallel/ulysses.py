@@ -105,13 +105,18 @@ def _peer_buffers(key, shapes, dtype, device, group):
 
 
 def default_head_pieces(local_heads: int, seq: int = 1 << 30, batch: int = 1, limit: int = 8):
-    """Sizes of the pieces the local heads are cut into: as many pieces (at most `limit`) as still leave
-    each about four waves of attention thread blocks (one block per 256 query rows of a head, 148 SMs),
-    the smaller pieces first -- the first piece's exchange is the one nothing hides.  75 600 tokens:
-    5 heads -> [2, 3], 10 -> [2] * 5, 20 -> [2, 2, 2, 2, 3, 3, 3, 3]."""
+    """Sizes of the pieces the local heads are cut into.  A piece should keep about eight waves of attention
+    thread blocks (one block per 256 query rows of a head, 148 SMs): smaller pieces lose more to their partial
+    last wave and to the exchange kernels that take SMs beside them than their overlap wins back (75 600
+    tokens, 2 GPUs: eight pieces of 2-3 heads measured 63.3 ms per layer, five pieces of 4 heads 54.8 ms).
+    When the local heads make fewer than two such pieces but at least two pieces of four waves, they are cut
+    in two anyway, the smaller first, so that every world size has some overlap -- the first piece's exchange
+    is the one nothing hides.  75 600 tokens: 20 heads -> [4] * 5, 10 -> [5, 5], 5 -> [2, 3]."""
     blocks_per_head = batch * ((seq + 255) // 256)
-    min_heads = max(1, -(-4 * 148 // blocks_per_head))
+    min_heads = max(1, -(-8 * 148 // blocks_per_head))
     pieces = max(1, min(limit, local_heads // min_heads))
+    if pieces == 1 and local_heads >= 2 * max(1, -(-min_heads // 2)) and local_heads > 1:
+        pieces = 2
     base, extra = divmod(local_heads, pieces)
     return [base] * (pieces - extra) + [base + 1] * extra
 
@@ -301,7 +306,7 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
                 _piece_ready(c, head0, sizes[c], comm)  # e.g. wait for the piece's heads to arrive from the host
             with timer.span("pack", comm):
                 _move((qr, kr, vr), send, rows, world, n_loc, head0, sizes[c], rope=rope_args,
-                      thread_blocks=0 if c == 0 else 32)
+                      thread_blocks=0)
             with timer.span("exchange_in", comm):
                 dist.all_to_all_single(recv, send, group=group)
             return record(comm)
@@ -400,7 +405,7 @@ def _ulysses_peer(qr, kr, vr, out, outr, sizes, world, rank, rows, n_loc, d, sca
                 if rope_args is not None:
                     cos, sin, mode = rope_args
                 _cabi.ulysses_move((qr, kr, vr), ptrs, 3 * h * d, rows, world, n_loc, head0[c], h, cos=cos, sin=sin,
-                                   rope_mode=mode, thread_blocks=0 if c == 0 else 32)
+                                   rope_mode=mode, thread_blocks=0)
             with timer.span("exchange_in", comm):
                 order_ranks("comm")
             ev = torch.cuda.Event()
