@@ -2,11 +2,14 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
 
-A step is one self-attention layer of the Wan2.1-14B 720p shape (B1 N40 S75600 D128, bf16, dense):
-117.05 TFLOP.  N = 1 runs the dense tcgen05 kernel on one GPU; N > 1 (under torchrun, one rank per
-GPU) runs the same layer sequence-parallel with the Ulysses wrapper, so the total work is fixed
-("strong" scaling) and `value` is the whole job's dense-equivalent TFLOP/s.  Rank 0 prints one JSON
-line.  Inputs are seeded synthetic tensors of the named shapes (no dataset exists for this path);
+The unit of work is one self-attention layer of the Wan2.1-14B 720p shape (B1 N40 S75600 D128, bf16,
+dense): 117.05 TFLOP.  N = 1 runs the dense tcgen05 kernel on one GPU, one layer per step; N > 1 (under
+torchrun, one rank per GPU) runs the same layer sequence-parallel with the Ulysses wrapper, a step
+repeating the layer (`config.layers_per_step`) so that the timed region lasts about two seconds at
+every N; the total work per layer is fixed ("strong" scaling) and `value` is the whole job's
+dense-equivalent TFLOP/s.  Before the timed region every rank of an N > 1 run checks its Ulysses output
+bit for bit against the single-GPU kernel on the unsharded tensors (`config.parity`).  Rank 0 prints one
+JSON line.  Inputs are seeded synthetic tensors of the named shapes (no dataset exists for this path);
 3.1 GB of operands per step exceed the 126 MB L2, so no L2 flush is needed between steps.
 
 Other single-GPU workloads of the same path (`--workload sparse|sparse_layer|fp8|fp8_layer|mask|quant|rotate_quant|rearrange|estimate|ada_layer|c2`) print the
