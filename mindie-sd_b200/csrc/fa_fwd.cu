@@ -72,7 +72,10 @@ constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) compiles to:
 //   0  exponentials against the running max right away, overflow caught by a row-sum test, P handed over whole
 //   2  block max first; P stored chunk by chunk as it is computed and handed over after 96 and 128
 //      keys; the row sum is taken after the hand-over, off the path the MMA thread waits on
-// Both pass the same tests and measure the same (105.7 ms each on one GPU); 0 is built.
+//   3  as 0, but the scores are read from tensor memory 32 columns at a time, the next read in flight while
+//      the exponentials of the previous columns are taken (64 score registers alive instead of 128); the
+//      first block of a row and any block whose row-sum test fails take the whole-row path of 0
+// 0 and 2 pass the same tests and measure the same (105.7 ms each on one GPU).
 #ifndef SDB_FA_BF16_MODE
 #define SDB_FA_BF16_MODE 0
 #endif
@@ -92,7 +95,8 @@ constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) compiles to:
 #define SDB_FA_DEFER_SUM_FP8 0
 #endif
 constexpr int kBf16Mode = SDB_FA_BF16_MODE;
-static_assert(kBf16Mode == 0 || kBf16Mode == 2, "SDB_FA_BF16_MODE");
+static_assert(kBf16Mode == 0 || kBf16Mode == 2 || kBf16Mode == 3, "SDB_FA_BF16_MODE");
+constexpr bool kStream = kBf16Mode == 3;
 constexpr bool kMaxFirst = kBf16Mode == 2;
 constexpr int kRegsSoftmax = SDB_FA_REGS_SOFTMAX;
 constexpr int kRegsOther = SDB_FA_REGS_OTHER;
@@ -573,33 +577,44 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             }
         }
 
+        // scale blocks are 128, 256 or 512 tokens: key block j uses scale j >> shift
+        int k_shift = 0, v_shift = 0;
+        if constexpr (kFp8) {
+            k_shift = 31 - __clz(p.k_scale_block / kTile);
+            if (p.v_scale_block > 0) v_shift = 31 - __clz(p.v_scale_block / kTile);
+        }
         float m_run = -INFINITY;  // running row max, in log2 units of the scaled scores
         float l_run = 0.0f;
         int cnt = 0;
         bool ok = true;
         for (int j = 0; j < nkb; ++j) {
             if (!my_flags[j]) continue;
+            // The block's dequantisation scales are fetched (and the v scale's logarithm taken) before the wait
+            // for its scores: their latency is spent while the MMA thread still works on the block.
+            float mult = p.scale_log2;
+            float v_off = 0.0f, l_fix = 1.0f;
+            if constexpr (kFp8) {
+                mult *= q_sc * k_sc[j >> k_shift];
+                if (v_blk) {
+                    const float r = fmaxf(v_blk[j >> v_shift], 1e-30f) / v_ref;
+                    v_off = log2f(r);
+                    l_fix = 1.0f / r;
+                }
+            }
             ok = __all_sync(0xffffffffu, mbar_wait(bar_s(t), static_cast<uint32_t>(cnt) & 1u, abort_flag, 20 + t, wait_us));
             if (!ok) break;
             tc_fence_after();
             if (row_in_tile == 64) SDB_TR(t, j, 0);
 
             uint32_t s[4][32];
+            constexpr bool kWholeRowFirst = kFp8 || !kStream;  // the streamed form reads the scores as it goes
+            if constexpr (kWholeRowFirst) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(taddr_s + c * 32, s[c]);
-            tmem_wait_ld();
+                for (int c = 0; c < 4; ++c) tmem_ld32(taddr_s + c * 32, s[c]);
+                tmem_wait_ld();
+            }
             if (row_in_tile == 64) SDB_TR(t, j, 1);
 
-            float mult = p.scale_log2;
-            float v_off = 0.0f, l_fix = 1.0f;
-            if constexpr (kFp8) {
-                mult *= q_sc * k_sc[(j * kTile) / p.k_scale_block];
-                if (v_blk) {
-                    const float r = fmaxf(v_blk[(j * kTile) / p.v_scale_block], 1e-30f) / v_ref;
-                    v_off = log2f(r);
-                    l_fix = 1.0f / r;
-                }
-            }
             // Columns this row may not see in this block: beyond the end of the keys (last block) or, with
             // causal attention, beyond the row's own position (the blocks the tile's diagonal crosses).
             bool masked = j == nkb - 1 && tail_valid < kTile;  // warp-uniform
@@ -615,7 +630,8 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     for (int i = 0; i < 32; ++i)
                         if (c * 32 + i >= n_seen) s[c][i] = 0xff800000u;  // -inf
             };
-            if (masked) mask_scores();
+            if constexpr (kWholeRowFirst)
+                if (masked) mask_scores();
             // The four exponentials of one group: x = s * mult - m as packed pairs, the first pair on the
             // exponent unit, the second there too or -- for kPoly of every eight groups -- on the FMA pipe.
             constexpr int kPoly = kFp8 ? SDB_FA_POLY_FP8 : SDB_FA_POLY;
@@ -656,7 +672,99 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(mx8[i], __uint_as_float(s[3][i + 24]));
                 return fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             };
-            if constexpr (!kFp8 && !kMaxFirst) {
+            if constexpr (!kFp8 && kStream) {
+                const uint64_t mult2 = pack2(mult, mult);
+                uint32_t pk[4][16];
+                float sum = 0.0f;
+                // 32 columns: exponentials against the running max, packed, summed.
+                auto chunk = [&](uint32_t (&sc)[32], auto cc, uint64_t negm2, uint64_t (&sum2)[2]) {
+                    constexpr int c = decltype(cc)::value;
+                    if (masked) {
+    #pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i >= n_seen) sc[i] = 0xff800000u;  // -inf
+                    }
+    #pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float e0, e1, e2, e3;
+                        unpack2(fma2(pack2(__uint_as_float(sc[4 * i]), __uint_as_float(sc[4 * i + 1])), mult2, negm2), e0, e1);
+                        e0 = ex2_approx(e0);
+                        e1 = ex2_approx(e1);
+                        unpack2(fma2(pack2(__uint_as_float(sc[4 * i + 2]), __uint_as_float(sc[4 * i + 3])), mult2, negm2), e2, e3);
+                        e2 = ex2_approx(e2);
+                        e3 = ex2_approx(e3);
+                        sum2[0] = add2(sum2[0], pack2(e0, e1));
+                        sum2[1] = add2(sum2[1], pack2(e2, e3));
+                        pk[c][2 * i] = pack_pair(e0, e1, kIn);
+                        pk[c][2 * i + 1] = pack_pair(e2, e3, kIn);
+                    }
+                };
+                bool whole_row = cnt == 0;  // the first block has no running max yet
+                if (!whole_row) {
+                    const float neg_m = -m_run;
+                    const uint64_t negm2 = pack2(neg_m, neg_m);
+                    uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
+                    tmem_ld32(taddr_s, s[0]);
+                    tmem_wait_ld();
+                    tmem_ld32(taddr_s + 32, s[1]);  // in flight under the first 32 exponentials
+                    chunk(s[0], std::integral_constant<int, 0>{}, negm2, sum2);
+                    tmem_wait_ld();
+                    tmem_ld32(taddr_s + 64, s[0]);
+                    chunk(s[1], std::integral_constant<int, 1>{}, negm2, sum2);
+                    tmem_wait_ld();
+                    tmem_ld32(taddr_s + 96, s[1]);
+                    chunk(s[0], std::integral_constant<int, 2>{}, negm2, sum2);
+                    tmem_wait_ld();
+                    chunk(s[1], std::integral_constant<int, 3>{}, negm2, sum2);
+                    float a, b;
+                    unpack2(add2(sum2[0], sum2[1]), a, b);
+                    sum = a + b;
+                    // Every probability is non-negative, so a row sum within 2^lag bounds each of them.
+                    whole_row = __any_sync(0xffffffffu, !(sum <= kRedoSum));
+                }
+                if (whole_row) {
+                    // Nothing has been stored over the scores yet: fetch the row, take its max, rescale what
+                    // has been accumulated so far and take the exponentials against the new max.
+    #pragma unroll
+                    for (int c = 0; c < 4; ++c) tmem_ld32(taddr_s + c * 32, s[c]);
+                    tmem_wait_ld();
+                    if (masked) mask_scores();
+                    const float m_new = fmaxf(fmaxf(m_run, row_max() * mult), -3.0e38f);
+                    const float alpha = ex2_approx(m_run - m_new);  // 0 on the first block
+                    m_run = m_new;
+                    l_run *= alpha;
+                    if (cnt > 0) {  // the previous P V product has finished and this block's has not been handed over
+    #pragma unroll 1
+                        for (int c = 0; c < kHeadDim / 8; ++c) {
+                            uint32_t o[8];
+                            tmem_ld8(taddr_o + c * 8, o);
+                            tmem_wait_ld();
+    #pragma unroll
+                            for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st8(taddr_o + c * 8, o);
+                        }
+                    }
+                    const float neg_m = -m_run;
+                    const uint64_t negm2 = pack2(neg_m, neg_m);
+                    uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
+                    const bool was_masked = masked;
+                    masked = false;  // mask_scores has been applied to the whole row
+                    chunk(s[0], std::integral_constant<int, 0>{}, negm2, sum2);
+                    chunk(s[1], std::integral_constant<int, 1>{}, negm2, sum2);
+                    chunk(s[2], std::integral_constant<int, 2>{}, negm2, sum2);
+                    chunk(s[3], std::integral_constant<int, 3>{}, negm2, sum2);
+                    masked = was_masked;
+                    float a, b;
+                    unpack2(add2(sum2[0], sum2[1]), a, b);
+                    sum = a + b;
+                }
+    #pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_st16(taddr_s + c * 16, pk[c]);
+                l_run += sum;
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar_p(t, 1));
+            } else if constexpr (!kFp8 && !kMaxFirst) {
                 // The probabilities are taken against the running max right away and kept in registers; the
                 // scores die as they are consumed.  Every probability is non-negative, so a row sum within
                 // 2^lag bounds each of them: only if that test fails somewhere in the warp -- rare after the
