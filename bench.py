@@ -12,7 +12,7 @@ bit for bit against the single-GPU kernel on the unsharded tensors (`config.pari
 JSON line.  Inputs are seeded synthetic tensors of the named shapes (no dataset exists for this path);
 3.1 GB of operands per step exceed the 126 MB L2, so no L2 flush is needed between steps.
 
-Other single-GPU workloads of the same path (`--workload sparse|sparse_layer|fp8|fp8_layer|mask|quant|rotate_quant|rearrange|estimate|ada_layer|c2`) print the
+Other single-GPU workloads of the same path (`--workload sparse|sparse_layer|fp8|fp8_layer|mask|quant|rotate_quant|rearrange|estimate|ada_layer|c2|ulysses_move|ulysses_move_rope`) print the
 same kind of line for their kernel; `--impl reference` times the CPU oracle (the reference's
 unfused torch formula) on the host cores for the same metric.
 """
@@ -38,7 +38,7 @@ import torch  # noqa: E402
 HEAD_DIM = 128
 # DRAM bytes one launch of the dense kernel moves at the benchmark shape, from one ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture has been taken.
-DENSE_DRAM_TRAFFIC_BYTES = 3.325e9  # 332.5 MB captured at 4 heads, scaled by 10 (traffic is per head)
+DENSE_DRAM_TRAFFIC_BYTES = 3.194e9  # 319.4 MB captured at 4 heads (259.3 read + 60.1 written), scaled by 10 (traffic is per head)
 
 
 def measured_peaks():
@@ -503,6 +503,24 @@ def single_gpu_workload(args, device):
         work = q.numel() * 4.0
         unit, bound = "GB/s", "hbm"
         label = "RainFusion window permutation of one operand, B1 N40 S75600 D128"
+    elif name in ("ulysses_move", "ulysses_move_rope"):
+        # The re-shard kernel of the sequence-parallel layer on one GPU at the 8-GPU shape: this rank's
+        # 9450 token rows of q, k, v, a piece of 3 local heads packed for 8 destinations (all local here).
+        del q, k, v
+        world, rows, piece = 8, cfg.seq // 8, 3
+        g = torch.Generator(device=device).manual_seed(0)
+        q, k, v = (torch.randn(rows, cfg.heads, HEAD_DIM, device=device, dtype=torch.bfloat16, generator=g) for _ in range(3))
+        send = torch.empty(world, rows, 3 * piece, HEAD_DIM, device=device, dtype=torch.bfloat16)
+        ptrs = [send[r].data_ptr() for r in range(world)]
+        kw = {}
+        if name == "ulysses_move_rope":
+            cos, sin = (torch.randn(rows, HEAD_DIM, device=device, generator=g) for _ in range(2))
+            kw = dict(cos=cos, sin=sin, rope_mode=1)
+        step = lambda: _cabi.ulysses_move((q, k, v), ptrs, send.stride(1), rows, world, cfg.heads // world, 0, piece, **kw)  # noqa: E731
+        work = 2.0 * send.numel() * 2  # every packed element is read once and written once
+        unit, bound = "GB/s", "hbm"
+        label = ("Ulysses re-shard kernel, one piece of 3 local heads of q, k, v for 8 destinations, 9450 rows x 40 heads x 128"
+                 + (", rotary embedding applied on the way" if kw else "") + "; 174 MB per launch, partly L2-resident between launches")
     else:
         raise SystemExit(f"unknown workload {name}")
     sampler = ClockSampler(physical_gpu_index(device.index))

@@ -49,35 +49,21 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
 // ---- build-time choices, each measured at the benchmark shape (B1 N40 S75600, bf16 unless noted) ----------
 //
-// Register re-split between the warpgroups after the roles part (setmaxnreg).  The registers a warpgroup
-// may take are the ones another warpgroup of the SAME thread block gave back: the pool is what the launch
-// gave the block (threads x registers per thread as compiled, 384 x 168), not the SM's register file.  A
-// request beyond it never returns -- there is no time limit on that wait -- so the sum is checked below and
-// again at launch.  Measured: no difference (103.3-103.9 ms without, 104.0-105.0 ms with 216 / 72), so the
-// plain launch allocation is built.
-#ifndef SDB_FA_RESPLIT
-#define SDB_FA_RESPLIT 0
-#endif
-#ifndef SDB_FA_RESPLIT_FP8
-#define SDB_FA_RESPLIT_FP8 0
-#endif
-#ifndef SDB_FA_REGS_SOFTMAX
-#define SDB_FA_REGS_SOFTMAX 216
-#endif
-#ifndef SDB_FA_REGS_OTHER
-#define SDB_FA_REGS_OTHER 72
-#endif
-constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) compiles to: 65536 / 384 rounded down to 8
-// How the softmax warps treat a block of two-byte operands (e4m3 always uses the second form):
-//   0  exponentials against the running max right away, overflow caught by a row-sum test, P handed over whole
+// How the softmax warps treat a block of two-byte operands (e4m3 always takes the block max first):
+//   0  exponentials against the running max right away, overflow caught by a row-sum test, P handed over
+//      whole; the first block's max, the masking of a partial block and the redo are inline
 //   2  block max first; P stored chunk by chunk as it is computed and handed over after 96 and 128
 //      keys; the row sum is taken after the hand-over, off the path the MMA thread waits on
-//   3  as 0, but the scores are read from tensor memory 32 columns at a time, the next read in flight while
-//      the exponentials of the previous columns are taken (64 score registers alive instead of 128); the
-//      first block of a row and any block whose row-sum test fails take the whole-row path of 0
-// 0 and 2 pass the same tests and measure the same (105.7 ms each on one GPU).
+//   4  as 0, with everything rare -- the first block's max, the masking (done where the scores lie, in
+//      tensor memory), the redo's max and the rescale of O -- in out-of-line functions, so that the loop
+//      over the key blocks holds one copy of the exponential pass and nothing else
+//   5  as 4, the scores read 32 columns at a time with the next read in flight under the exponentials
+// Measured, all builds alternating in one process on one GPU: 0: 102.6 ms, 2: 103.7 ms, 4: 98.3-99.7 ms,
+// 5: 98.5-100.4 ms (the earlier kernel: 106.4-107.8 ms).  The code the compiler emits for the loop is
+// sensitive to what else is inlined into it: the same pass is 4 % faster with the rare paths out of line, and
+// an extra polling loop in front of every barrier wait cost 6 %.
 #ifndef SDB_FA_BF16_MODE
-#define SDB_FA_BF16_MODE 0
+#define SDB_FA_BF16_MODE 4
 #endif
 // Of the eight groups of four scores in a 32-column chunk, how many take the exponentials of their
 // second pair on the FMA pipe (ex2_poly2) instead of the exponent unit: 8 = half of all exponentials.
@@ -94,14 +80,15 @@ constexpr int kLaunchRegs = 168;  // what __launch_bounds__(384, 1) compiles to:
 #ifndef SDB_FA_DEFER_SUM_FP8
 #define SDB_FA_DEFER_SUM_FP8 0
 #endif
+// Not built: a re-split of the registers between the warpgroups after the roles part (setmaxnreg, 216 for
+// the softmax warps and 72 for the others out of the 384 x 168 the launch gives the thread block).  It
+// measured the same or slower (104.0-105.0 ms against 103.3-103.9 ms) and does not assemble together
+// with out-of-line functions.
 constexpr int kBf16Mode = SDB_FA_BF16_MODE;
-static_assert(kBf16Mode == 0 || kBf16Mode == 2 || kBf16Mode == 3, "SDB_FA_BF16_MODE");
-constexpr bool kStream = kBf16Mode == 3;
+static_assert(kBf16Mode == 0 || kBf16Mode == 2 || kBf16Mode == 4 || kBf16Mode == 5, "SDB_FA_BF16_MODE");
+constexpr bool kLean = kBf16Mode == 4 || kBf16Mode == 5;
+constexpr bool kLeanStream = kBf16Mode == 5;
 constexpr bool kMaxFirst = kBf16Mode == 2;
-constexpr int kRegsSoftmax = SDB_FA_REGS_SOFTMAX;
-constexpr int kRegsOther = SDB_FA_REGS_OTHER;
-static_assert(2 * 128 * kRegsSoftmax + 128 * kRegsOther <= 384 * kLaunchRegs, "register pool of one thread block");
-static_assert(kRegsSoftmax % 8 == 0 && kRegsOther % 8 == 0 && kRegsOther >= 24 && kRegsSoftmax <= 256, "setmaxnreg operand");
 constexpr float kRescaleThreshold = 8.0f;  // log2 units the running max may lag before O is rescaled
 constexpr float kFp8PShiftLog2 = 8.0f;     // e4m3 probabilities are stored as p * 2^8
 constexpr float kFp8Lag = 0.75f;           // 2^8.75 = 431 still fits e4m3 (max 448)
@@ -166,13 +153,53 @@ __device__ __forceinline__ void poison_row(const FaParams& p, int batch, int hea
     if (p.lse) p.lse[batch * p.lse_stride[0] + head * p.lse_stride[1] + q_row * p.lse_stride[2]] = __int_as_float(0x7fc00000);
 }
 
+// Rare work of a score block, kept out of line so that it costs the hot loop neither registers nor code.
+// Fetches the calling row's 128 scores from tensor memory, turns the ones from column n_seen on into
+// -inf IN tensor memory (so that every later read sees them masked) and returns the row's maximum.
+__device__ __noinline__ float rare_row_max(uint32_t taddr_s, int n_seen) {
+    float mx = -INFINITY;
+    bool stored = false;
+#pragma unroll 1
+    for (int c = 0; c < 16; ++c) {
+        uint32_t s[8];
+        tmem_ld8(taddr_s + c * 8, s);
+        tmem_wait_ld();
+        // The rows of a warp may see different numbers of columns (causal diagonal); the store is
+        // warp-collective, so the warp decides together and a row with nothing to mask writes back what it read.
+        if (__any_sync(0xffffffffu, c * 8 + 8 > n_seen)) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (c * 8 + i >= n_seen) s[i] = 0xff800000u;
+            tmem_st8(taddr_s + c * 8, s);
+            stored = true;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+    }
+    if (stored) tmem_wait_st();
+    return mx;
+}
+
+// O *= alpha for the calling row (the accumulator is at rest).
+__device__ __noinline__ void rare_rescale_o(uint32_t taddr_o, float alpha) {
+#pragma unroll 1
+    for (int c = 0; c < kHeadDim / 8; ++c) {
+        uint32_t o[8];
+        tmem_ld8(taddr_o + c * 8, o);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st8(taddr_o + c * 8, o);
+    }
+    tmem_wait_st();
+}
+
 }  // namespace
 
 // kIn: element type of q/k/v and of the stored probabilities (0 bf16, 1 fp16, 3 e4m3).
 template <int kIn>
 __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_constant__ FaParams p) {
     constexpr bool kFp8 = kIn == 3;
-    constexpr bool kResplit = (SDB_FA_RESPLIT_FP8 || !kFp8) && SDB_FA_RESPLIT;  // whether the warpgroups re-split their registers
     constexpr bool kSplit = kFp8 || kMaxFirst;  // P is handed to the MMA thread in two parts
     // 32-key chunks of a block in the first part: half of the block, or three quarters when the
     // exponentials of a two-byte block are taken max-first (the second part's product is then short).
@@ -331,12 +358,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         return j < nkb ? j : -1;
     };
 
-    // The softmax warps hold a whole score row and the packed probabilities of a block in registers
-    // (about 200 live values); the loader, the MMA thread and the two idle warps need a few dozen.
-    // The launch gives every thread 168: the last warpgroup hands most of its registers back and
-    // each softmax warpgroup takes its share.
     if (warp >= 8) {
-      if constexpr (kResplit) warpgroup_reg_dec<kRegsOther>();
       if (warp == kLoadWarp && p.perm_on == 1) {
         // ---- TMA producer, RainFusion window permutation applied on the fly ---------------------
         // q, k and v are in their original token order; the tiles the other roles see hold the PERMUTED
@@ -541,7 +563,6 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         }
       }
     } else {
-        if constexpr (kResplit) warpgroup_reg_inc<kRegsSoftmax>();
         // ---- softmax, O rescale, epilogue: one query row per thread ------------------------------
         const int t = warp >> 2;  // tile of this warpgroup
         const int row_in_tile = tid & (kTile - 1);
@@ -606,15 +627,6 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             tc_fence_after();
             if (row_in_tile == 64) SDB_TR(t, j, 0);
 
-            uint32_t s[4][32];
-            constexpr bool kWholeRowFirst = kFp8 || !kStream;  // the streamed form reads the scores as it goes
-            if constexpr (kWholeRowFirst) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld32(taddr_s + c * 32, s[c]);
-                tmem_wait_ld();
-            }
-            if (row_in_tile == 64) SDB_TR(t, j, 1);
-
             // Columns this row may not see in this block: beyond the end of the keys (last block) or, with
             // causal attention, beyond the row's own position (the blocks the tile's diagonal crosses).
             bool masked = j == nkb - 1 && tail_valid < kTile;  // warp-uniform
@@ -623,6 +635,16 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 masked = true;
                 n_seen = min(n_seen, q_row + causal_off - j * kTile + 1);
             }
+            uint32_t s[4][32];
+            constexpr bool kWholeRowFirst = kFp8 || !kLean;  // the lean forms fetch the scores inside their pass loop
+            if constexpr (kWholeRowFirst) {
+                if constexpr (kFp8)
+                    if (masked) rare_row_max(taddr_s, n_seen);  // masks the scores where they lie
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld32(taddr_s + c * 32, s[c]);
+                tmem_wait_ld();
+            }
+            if (row_in_tile == 64) SDB_TR(t, j, 1);
             auto mask_scores = [&]() {
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
@@ -630,7 +652,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     for (int i = 0; i < 32; ++i)
                         if (c * 32 + i >= n_seen) s[c][i] = 0xff800000u;  // -inf
             };
-            if constexpr (kWholeRowFirst)
+            if constexpr (kWholeRowFirst && !kFp8)
                 if (masked) mask_scores();
             // The four exponentials of one group: x = s * mult - m as packed pairs, the first pair on the
             // exponent unit, the second there too or -- for kPoly of every eight groups -- on the FMA pipe.
@@ -672,91 +694,68 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                 for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(mx8[i], __uint_as_float(s[3][i + 24]));
                 return fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             };
-            if constexpr (!kFp8 && kStream) {
+            if constexpr (!kFp8 && kLean) {
+                // As the next form, with everything that is rare -- the first block's max, masking, the redo --
+                // in out-of-line functions that work on tensor memory.
+                const bool first = cnt == 0;
+                if (masked || first) {
+                    const float mx = rare_row_max(taddr_s, masked ? n_seen : kTile);
+                    if (first) m_run = fmaxf(mx * mult, -3.0e38f);
+                }
                 const uint64_t mult2 = pack2(mult, mult);
                 uint32_t pk[4][16];
                 float sum = 0.0f;
-                // 32 columns: exponentials against the running max, packed, summed.
-                auto chunk = [&](uint32_t (&sc)[32], auto cc, uint64_t negm2, uint64_t (&sum2)[2]) {
-                    constexpr int c = decltype(cc)::value;
-                    if (masked) {
-    #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (c * 32 + i >= n_seen) sc[i] = 0xff800000u;  // -inf
-                    }
-    #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        float e0, e1, e2, e3;
-                        unpack2(fma2(pack2(__uint_as_float(sc[4 * i]), __uint_as_float(sc[4 * i + 1])), mult2, negm2), e0, e1);
-                        e0 = ex2_approx(e0);
-                        e1 = ex2_approx(e1);
-                        unpack2(fma2(pack2(__uint_as_float(sc[4 * i + 2]), __uint_as_float(sc[4 * i + 3])), mult2, negm2), e2, e3);
-                        e2 = ex2_approx(e2);
-                        e3 = ex2_approx(e3);
-                        sum2[0] = add2(sum2[0], pack2(e0, e1));
-                        sum2[1] = add2(sum2[1], pack2(e2, e3));
-                        pk[c][2 * i] = pack_pair(e0, e1, kIn);
-                        pk[c][2 * i + 1] = pack_pair(e2, e3, kIn);
-                    }
-                };
-                bool whole_row = cnt == 0;  // the first block has no running max yet
-                if (!whole_row) {
+    #pragma unroll 1
+                for (int pass = 0; pass < 2; ++pass) {
                     const float neg_m = -m_run;
                     const uint64_t negm2 = pack2(neg_m, neg_m);
                     uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
-                    tmem_ld32(taddr_s, s[0]);
-                    tmem_wait_ld();
-                    tmem_ld32(taddr_s + 32, s[1]);  // in flight under the first 32 exponentials
-                    chunk(s[0], std::integral_constant<int, 0>{}, negm2, sum2);
-                    tmem_wait_ld();
-                    tmem_ld32(taddr_s + 64, s[0]);
-                    chunk(s[1], std::integral_constant<int, 1>{}, negm2, sum2);
-                    tmem_wait_ld();
-                    tmem_ld32(taddr_s + 96, s[1]);
-                    chunk(s[0], std::integral_constant<int, 2>{}, negm2, sum2);
-                    tmem_wait_ld();
-                    chunk(s[1], std::integral_constant<int, 3>{}, negm2, sum2);
-                    float a, b;
-                    unpack2(add2(sum2[0], sum2[1]), a, b);
-                    sum = a + b;
-                    // Every probability is non-negative, so a row sum within 2^lag bounds each of them.
-                    whole_row = __any_sync(0xffffffffu, !(sum <= kRedoSum));
-                }
-                if (whole_row) {
-                    // Nothing has been stored over the scores yet: fetch the row, take its max, rescale what
-                    // has been accumulated so far and take the exponentials against the new max.
+                    if constexpr (kLeanStream) {
+                        // 32 columns at a time, the next read in flight under the exponentials of the previous ones
+                        tmem_ld32(taddr_s, s[0]);
     #pragma unroll
-                    for (int c = 0; c < 4; ++c) tmem_ld32(taddr_s + c * 32, s[c]);
-                    tmem_wait_ld();
-                    if (masked) mask_scores();
-                    const float m_new = fmaxf(fmaxf(m_run, row_max() * mult), -3.0e38f);
-                    const float alpha = ex2_approx(m_run - m_new);  // 0 on the first block
-                    m_run = m_new;
-                    l_run *= alpha;
-                    if (cnt > 0) {  // the previous P V product has finished and this block's has not been handed over
-    #pragma unroll 1
-                        for (int c = 0; c < kHeadDim / 8; ++c) {
-                            uint32_t o[8];
-                            tmem_ld8(taddr_o + c * 8, o);
+                        for (int c = 0; c < 4; ++c) {
                             tmem_wait_ld();
+                            if (c < 3) tmem_ld32(taddr_s + (c + 1) * 32, s[(c + 1) & 1]);
     #pragma unroll
-                            for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                            tmem_st8(taddr_o + c * 8, o);
+                            for (int i = 0; i < 8; ++i) {
+                                float e0, e1, e2, e3;
+                                exp4(std::true_type{}, c & 1, i, mult2, negm2, e0, e1, e2, e3);
+                                sum2[0] = add2(sum2[0], pack2(e0, e1));
+                                sum2[1] = add2(sum2[1], pack2(e2, e3));
+                                pk[c][2 * i] = pack_pair(e0, e1, kIn);
+                                pk[c][2 * i + 1] = pack_pair(e2, e3, kIn);
+                            }
+                        }
+                    } else {
+    #pragma unroll
+                        for (int c = 0; c < 4; ++c) tmem_ld32(taddr_s + c * 32, s[c]);
+                        tmem_wait_ld();
+    #pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+    #pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                float e0, e1, e2, e3;
+                                exp4(std::true_type{}, c, i, mult2, negm2, e0, e1, e2, e3);
+                                sum2[0] = add2(sum2[0], pack2(e0, e1));
+                                sum2[1] = add2(sum2[1], pack2(e2, e3));
+                                pk[c][2 * i] = pack_pair(e0, e1, kIn);
+                                pk[c][2 * i + 1] = pack_pair(e2, e3, kIn);
+                            }
                         }
                     }
-                    const float neg_m = -m_run;
-                    const uint64_t negm2 = pack2(neg_m, neg_m);
-                    uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
-                    const bool was_masked = masked;
-                    masked = false;  // mask_scores has been applied to the whole row
-                    chunk(s[0], std::integral_constant<int, 0>{}, negm2, sum2);
-                    chunk(s[1], std::integral_constant<int, 1>{}, negm2, sum2);
-                    chunk(s[2], std::integral_constant<int, 2>{}, negm2, sum2);
-                    chunk(s[3], std::integral_constant<int, 3>{}, negm2, sum2);
-                    masked = was_masked;
-                    float a, b;
-                    unpack2(add2(sum2[0], sum2[1]), a, b);
-                    sum = a + b;
+                    {
+                        float a, b;
+                        unpack2(add2(sum2[0], sum2[1]), a, b);
+                        sum = a + b;
+                    }
+                    if (pass == 1 || first) break;
+                    if (!__any_sync(0xffffffffu, !(sum <= kRedoSum))) break;
+                    const float m_new = fmaxf(m_run, rare_row_max(taddr_s, kTile) * mult);
+                    const float alpha = ex2_approx(m_run - m_new);
+                    m_run = m_new;
+                    l_run *= alpha;
+                    rare_rescale_o(taddr_o, alpha);
                 }
     #pragma unroll
                 for (int c = 0; c < 4; ++c) tmem_st16(taddr_s + c * 16, pk[c]);
@@ -843,17 +842,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
                     // The (rare, after the first blocks) rescale of O must be over before the first half
                     // of P is handed to the MMA thread.  The scores of this block were issued behind the
                     // previous P V product, so that product has finished.
-                    if (cnt > 0) {  // eight columns at a time: the scores are live, registers are scarce here
-    #pragma unroll 1
-                        for (int c = 0; c < kHeadDim / 8; ++c) {
-                            uint32_t o[8];
-                            tmem_ld8(taddr_o + c * 8, o);
-                            tmem_wait_ld();
-    #pragma unroll
-                            for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                            tmem_st8(taddr_o + c * 8, o);
-                        }
-                    }
+                    if (cnt > 0) rare_rescale_o(taddr_o, alpha);
                 }
                 if (row_in_tile == 64) SDB_TR(t, j, 2);
                 // x = s * mult - m as packed pairs (one instruction per two scores), then ex2 and pack.
@@ -1014,14 +1003,6 @@ static cudaError_t launch_one(const FaParams& p, cudaStream_t stream) {
     const int smem = fa_fwd_smem_bytes(kIn == 3);
     cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<kIn>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    // The kernel's warpgroups re-split the registers the launch gives the block; if this build of the
-    // kernel was given fewer than the split assumes, the request would wait forever.  Refuse instead.
-    static const int launch_regs = [] {
-        cudaFuncAttributes attr;
-        return cudaFuncGetAttributes(&attr, fa_fwd_kernel<kIn>) == cudaSuccess ? attr.numRegs : 0;
-    }();
-    if (SDB_FA_RESPLIT && (SDB_FA_RESPLIT_FP8 || kIn != 3) && 2 * 128 * kRegsSoftmax + 128 * kRegsOther > kThreads * launch_regs)
-        return cudaErrorLaunchOutOfResources;
     // Packed sequences: every sequence rounds its tile pairs up, so seq_q / 256 + num_seqs bounds their number.
     const int pairs = p.cu_seqlens_q ? p.seq_q / (2 * kTile) + p.num_seqs : (p.seq_q + 2 * kTile - 1) / (2 * kTile);
     dim3 grid(pairs, p.heads, p.batch);

@@ -52,19 +52,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // give up together; the ones that start afterwards see the status word and leave).
 constexpr uint32_t kWaitLimitUs = 1000000u;
 
-
 // Waits for the phase with the given parity, for at most limit_us microseconds of wall-clock time
 // (the nanosecond timer of the device, which does not depend on the SM clock).  Returns false if
 // the wait gave up (limit reached, or another role of the thread block raised the abort flag); the
 // first to give up raises the flag and leaves `site` (a small number naming the wait) next to it.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site = 0,
                                           uint32_t limit_us = kWaitLimitUs) {
-    // Waits inside these kernels end within microseconds: a first phase polls without touching the timer
-    // or the flag, so the common case costs what a bare wait costs.  (Each attempt suspends the thread for a
-    // hardware-chosen while by itself.)
-#pragma unroll 1
-    for (int i = 0; i < 1024; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
+    // Kept small on purpose: this is inlined in front of every barrier wait of the kernels, and their hot
+    // loops measured 5 % slower with one more polling loop here.  (Each attempt suspends the thread for a
+    // hardware-chosen while by itself; the timer and the flag are looked at every 64 attempts.)
+    if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -90,18 +87,6 @@ __device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity, u
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63u) == 0u && global_timer_ns() - t0 > static_cast<uint64_t>(limit_us) * 1000u) return false;
     }
-}
-
-// Register budget of the calling warpgroup (four consecutive warps, all of which execute this):
-// a warpgroup that needs few registers hands them back so that another can take more than the
-// launch gave it.
-template <int kRegs>
-__device__ __forceinline__ void warpgroup_reg_dec() {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
-}
-template <int kRegs>
-__device__ __forceinline__ void warpgroup_reg_inc() {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
 }
 
 // ----------------------------------------------------------------------------------------------

@@ -106,6 +106,31 @@ def test_large_logits_do_not_overflow():
     _status_ok()
 
 
+@pytest.mark.parametrize("jump", ["lower_half", "upper_half", "one_key_lower", "one_key_upper", "every_block"])
+def test_row_max_jumps_inside_a_key_block(jump):
+    """The running max jumps far beyond its allowed lag in the first 64 keys of a block only, in the last 64
+    only, at a single key, or block after block: every way the kernel's speculative exponentials can fail
+    their row-sum test and be taken again."""
+    from mindiesd import _cabi
+    q = inputs.randn(63, 1, 2, 384, 128, dtype=torch.bfloat16) * 4
+    k = inputs.randn(64, 1, 2, 1280, 128, dtype=torch.bfloat16) * 4
+    v = inputs.randn(65, 1, 2, 1280, 128, dtype=torch.bfloat16)
+    if jump == "lower_half":
+        k[:, :, 512:576] *= 3
+    elif jump == "upper_half":
+        k[:, :, 704:768] *= 3
+    elif jump == "one_key_lower":
+        k[:, :, 640 + 5] *= 6
+    elif jump == "one_key_upper":
+        k[:, :, 640 + 100] *= 6
+    else:
+        for b in range(1, 10):
+            k[:, :, 128 * b + (37 if b % 2 else 91)] *= 1.0 + 0.6 * b
+    out = _cabi.attention(q.cuda(), k.cuda(), v.cuda())
+    _check(out, oa.attention_math(q.float(), k.float(), v.float(), head_first=True), max_abs=4e-2, mean_abs=4e-3)
+    _status_ok()
+
+
 def test_wan_1p3b_shape_rows():
     """Config C2 (B1 N12 S32760, RoPE'd q/k) on 2 heads: a fixed subset of query rows against the
     oracle, which is the full formula restricted to those rows."""
