@@ -234,8 +234,12 @@ def dense_or_ulysses(args, rank, world, device):
     parity = None
     pieces = None
     if world > 1:
-        from mindiesd.parallel import default_head_pieces
-        if args.ulysses_chunks:
+        from mindiesd.parallel import default_head_pieces, default_transport
+        if args.ulysses_transport is None:
+            args.ulysses_transport = default_transport(device=device)  # what the library picks on this group
+        if args.ulysses_pieces:
+            pieces = [int(x) for x in args.ulysses_pieces.split(",")]
+        elif args.ulysses_chunks:
             pieces = [cfg.heads // world // args.ulysses_chunks] * args.ulysses_chunks
         else:
             pieces = default_head_pieces(cfg.heads // world, cfg.seq)
@@ -292,6 +296,21 @@ def dense_or_ulysses(args, rank, world, device):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         phases = dict(zip(("pack_ms", "exchange_in_ms", "attention_ms", "exchange_out_ms", "unpack_ms"),
                           (round(x, 4) for x in t.tolist())))
+        # What the layer would cost if only this rank's attention ran: the same kernel on this rank's heads of
+        # the full sequence, repeated like the layer so that it runs in the same power state.  The difference
+        # to the timed layer is what the exchange costs after all overlap.
+        aq, ak, av = workloads.make_qkv(cfg, device, seed=1, heads=cfg.heads // world, layout="BSND")
+        ao = torch.empty_like(aq)
+
+        def alone():
+            for _ in range(layers):
+                _cabi.attention(aq, ak, av, head_first=False, out=ao)
+
+        alone_steps = max(2, args.steps // 2)
+        a = torch.tensor([timed(alone, alone_steps, 1, barrier) / (alone_steps * layers)], dtype=torch.float64, device=device)
+        dist.all_reduce(a, op=dist.ReduceOp.MAX)
+        phases["attention_alone_ms"] = round(a.item(), 4)
+        del aq, ak, av, ao
 
     # End to end through the public Python API with host buffers: every step copies this rank's
     # q, k, v from pinned host memory and reads its output back, copies pipelined with the kernels.
@@ -311,7 +330,9 @@ def dense_or_ulysses(args, rank, world, device):
             attention_forward_host(hq, hk, hv, out=ho, head_chunks=e2e_chunks)
         else:
             from mindiesd.parallel import ulysses_attention_host
-            ulysses_attention_host(hq, hk, hv, out=ho, head_chunks=pieces)
+            # its own piece sizes unless they were given: the copies over PCIe want smaller pieces than NVLink does
+            ulysses_attention_host(hq, hk, hv, out=ho,
+                                   head_chunks=pieces if (args.ulysses_pieces or args.ulysses_chunks) else None)
 
     e2e_steps = max(1, args.steps)
     e2e_ms = timed(e2e_step, e2e_steps, 1, barrier) if not args.kernel_only else float("nan")
@@ -330,7 +351,7 @@ def dense_or_ulysses(args, rank, world, device):
     config = {"workload": WORKLOAD if not args.heads else WORKLOAD.replace("N40", f"N{cfg.heads}") + " [heads reduced]",
               "layout": "BSND",
               "parallelism": "single GPU" if world == 1 else
-              f"ulysses sp{world}, local heads in pieces of {pieces}, exchange over {args.ulysses_transport or 'nccl'}",
+              f"ulysses sp{world}, local heads in pieces of {pieces}, exchange over {args.ulysses_transport}",
               "layers_per_step": layers, "ms_per_layer": ms_layer, "flops_per_layer": cfg.flops,
               "l2": "operands (3.1 GB per layer) exceed L2; no flush",
               "tflops_per_gpu": value / world, "kernel_status": status}
@@ -340,10 +361,13 @@ def dense_or_ulysses(args, rank, world, device):
     if parity is not None:
         config["parity"] = parity
     if phases is not None:
-        exposed = max(0.0, ms_layer - phases["attention_ms"])
+        exposed = max(0.0, ms_layer - phases["attention_alone_ms"])
         config["phases_of_one_layer"] = dict(phases, exposed_ms=round(exposed, 4),
-                                             note="CUDA events of one untimed layer, max over ranks; exposed = "
-                                                  "timed ms per layer minus the attention kernels' own time")
+                                             note="pack .. unpack: CUDA events of one untimed layer, summed over its "
+                                                  "pieces (spans on different streams overlap), max over ranks; "
+                                                  "attention_alone: this rank's heads through the kernel with nothing "
+                                                  "else running, timed like the layer; exposed = timed ms per layer "
+                                                  "minus attention_alone")
     line = {
         "metric": "attention_dense_equiv_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -556,6 +580,7 @@ def main():
     ap.add_argument("--sparsity", type=float, default=0.75)
     ap.add_argument("--band", type=int, default=-1)
     ap.add_argument("--ulysses-chunks", type=int, default=0, help="head chunks per rank of the Ulysses leg (0: the API's default)")
+    ap.add_argument("--ulysses-pieces", default=None, help="local heads per piece, e.g. 2,8,8,2 (default: library choice)")
     ap.add_argument("--ulysses-transport", default=None, choices=[None, "nccl", "peer"],
                     help="how the Ulysses leg exchanges data (default: the API's)")
     ap.add_argument("--e2e-chunks", type=int, default=0, help="head chunks of the pipelined end-to-end leg (0: the API's default)")

@@ -42,7 +42,10 @@ namespace {
 
 constexpr int kTile = 128;         // rows of a query tile and of a key/value block
 constexpr int kHeadDim = 128;
-constexpr int kThreads = 384;  // 12 warps: three per scheduler partition of the SM
+#ifndef SDB_FA_THREADS
+#define SDB_FA_THREADS 384
+#endif
+constexpr int kThreads = SDB_FA_THREADS;  // 12 warps: three per scheduler partition of the SM (320: no idle warps)
 constexpr int kMmaWarp = 8;
 constexpr int kLoadWarp = 9;
 constexpr uint32_t kTmemCols = 512;

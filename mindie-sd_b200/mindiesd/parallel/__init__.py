@@ -1,5 +1,5 @@
 from .ulysses import (ulysses_attention, ulysses_attention_host, default_head_chunks, default_head_pieces,
-                      release_buffers)
+                      default_transport, release_buffers)
 
 __all__ = ["ulysses_attention", "ulysses_attention_host", "default_head_chunks", "default_head_pieces",
-           "release_buffers"]
+           "default_transport", "release_buffers"]

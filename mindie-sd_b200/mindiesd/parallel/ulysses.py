@@ -11,16 +11,19 @@ this is the same tensor contract -- BSND in, BSND out, `N % world_size == 0` -- 
   way -- and ONE all-to-all carries q, k and v together.  For B = 1 the receive buffer already is
   `[S, 3h, D]`, which the attention kernel reads through strides; it writes its output straight into
   the send buffer of the return exchange, and one kernel scatters the returned blocks into the result.
-* The exchange of piece c+1 and the return of piece c-1 run on a communication stream under piece
-  c's attention.  Pieces may be uneven (5 local heads -> 2 + 3), so that overlap exists at every
-  world size.
+* The exchange of piece c+1 runs on an inbound stream and the return of piece c-1, with the scatter into
+  the caller's output, on an outbound stream, both under piece c's attention; the pieces' attention
+  kernels alternate between the caller's stream and a second one, so that a piece's thread blocks fill
+  the SMs the previous piece's last wave leaves idle.  Pieces may be uneven (5 local heads -> 2 + 3), so
+  that overlap exists at every world size.
 * Send and receive buffers are allocated once per (shape, dtype, group) and reused by every call.
 * transport="peer": the ranks map each other's receive buffers (CUDA IPC) once, and then the re-shard
   kernel IS the all-to-all: it stores each destination's block straight into that rank's receive
   buffer over NVLink, and after attention every rank's scatter kernel loads the blocks it needs straight
   from its peers' output buffers.  No send buffers, no NCCL data movement: the only collective left is a
-  one-element all-reduce per piece that orders the ranks.  transport="nccl" (the default where the
-  mapping is not available) packs into a send buffer and calls all_to_all_single.
+  one-element all-reduce per piece that orders the ranks.  It is the default where the ranks of the group
+  share a host and can map each other's memory; transport="nccl" (otherwise, and for B > 1 or a custom
+  attention function) packs into a send buffer and calls all_to_all_single.
 """
 from __future__ import annotations
 
@@ -47,10 +50,15 @@ _COMM_STREAMS = {}
 _BUFFERS = {}
 
 
-def _comm_stream(device):
+def _side_streams(device):
+    """(inbound, outbound, second compute) streams of a device.  Inbound carries the re-shard kernels and the
+    exchange towards the attention, outbound the exchange back and the scatter into the caller's output, both
+    at high priority; the second compute stream takes every other piece's attention kernel, so that a piece's
+    thread blocks fill the SMs the previous piece's last wave leaves idle."""
     key = device.index if device.index is not None else torch.cuda.current_device()
     if key not in _COMM_STREAMS:
-        _COMM_STREAMS[key] = torch.cuda.Stream(device=device, priority=-1)
+        _COMM_STREAMS[key] = (torch.cuda.Stream(device=device, priority=-1), torch.cuda.Stream(device=device, priority=-1),
+                              torch.cuda.Stream(device=device))
     return _COMM_STREAMS[key]
 
 
@@ -104,18 +112,60 @@ def _peer_buffers(key, shapes, dtype, device, group):
     return cached
 
 
-def default_head_pieces(local_heads: int, seq: int = 1 << 30, batch: int = 1, limit: int = 8):
-    """Sizes of the pieces the local heads are cut into.  A piece should keep about eight waves of attention
-    thread blocks (one block per 256 query rows of a head, 148 SMs): smaller pieces lose more to their partial
-    last wave and to the exchange kernels that take SMs beside them than their overlap wins back (75 600
-    tokens, 2 GPUs: eight pieces of 2-3 heads measured 63.3 ms per layer, five pieces of 4 heads 54.8 ms).
-    When the local heads make fewer than two such pieces but at least two pieces of four waves, they are cut
-    in two anyway, the smaller first, so that every world size has some overlap -- the first piece's exchange
-    is the one nothing hides.  75 600 tokens: 20 heads -> [4] * 5, 10 -> [5, 5], 5 -> [2, 3]."""
+_TRANSPORT_CHOICE = {}
+
+
+def _default_transport(device, group, peer_capable_call: bool) -> str:
+    """"peer" where this call can use it and every rank of the group sits in one process group of one host
+    whose GPUs can map each other's memory; else "nccl".  MINDIESD_ULYSSES_TRANSPORT overrides.  The ranks
+    decide together, once per (device, group): each gathers every rank's host name and device index, checks peer
+    access from its own device, and the choice is "peer" only if every rank's check passed."""
+    import os
+    import socket
+    forced = os.environ.get("MINDIESD_ULYSSES_TRANSPORT")
+    if forced:
+        return forced
+    if not peer_capable_call:
+        return "nccl"
+    key = (device.index, id(group))
+    if key not in _TRANSPORT_CHOICE:
+        world = dist.get_world_size(group)
+        mine = (socket.gethostname(), device.index if device.index is not None else torch.cuda.current_device(),
+                torch.cuda.device_count())
+        seen = [None] * world
+        dist.all_gather_object(seen, mine, group=group)
+        ok = (len({h for h, _, _ in seen}) == 1 and len({i for _, i, _ in seen}) == world
+              and all(n == mine[2] and i < n for _, i, n in seen)
+              and all(i == mine[1] or torch.cuda.can_device_access_peer(mine[1], i) for _, i, _ in seen))
+        votes = [None] * world
+        dist.all_gather_object(votes, bool(ok), group=group)
+        _TRANSPORT_CHOICE[key] = "peer" if all(votes) else "nccl"
+    return _TRANSPORT_CHOICE[key]
+
+
+def default_transport(group=None, device=None) -> str:
+    """The transport `ulysses_attention(transport=None)` uses on this group for B = 1 CUDA operands and the
+    default attention kernel.  Collective: every rank of the group calls it."""
+    device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    return _default_transport(device, group, True)
+
+
+def default_head_pieces(local_heads: int, seq: int = 1 << 30, batch: int = 1, limit: int = 8, waves: int = 20,
+                        split_small: bool = False):
+    """Sizes of the pieces the local heads are cut into.  A piece keeps at least `waves` waves of attention
+    thread blocks (one block per 256 query rows of a head, 148 SMs).  Over NVLink the exchange of a whole
+    rank's heads costs a few hundred microseconds, less than what every further piece loses to its partial
+    last wave and to the exchange kernels that take SMs beside it, so pieces are large.  Measured at 75 600
+    tokens, per layer, peer transport: 2 GPUs [10, 10] 51.8 ms, [6, 7, 7] 52.1 ms, [4] * 5 52.5 ms; 4 GPUs [10]
+    26.1 ms, [5, 5] 26.4 ms; 8 GPUs [5] 13.1 ms, [2, 3] 13.6 ms.  20 waves give 20 heads -> [10, 10],
+    10 -> [10], 5 -> [5].
+    `split_small` cuts fewer heads than two such pieces in two anyway, the smaller first, where that leaves at
+    least half a piece each: the host-operand pipeline uses it with `waves=8`, because there the copies over
+    PCIe are what has to be hidden (20 heads -> [4] * 5, 10 -> [5, 5], 5 -> [2, 3])."""
     blocks_per_head = batch * ((seq + 255) // 256)
-    min_heads = max(1, -(-8 * 148 // blocks_per_head))
+    min_heads = max(1, -(-waves * 148 // blocks_per_head))
     pieces = max(1, min(limit, local_heads // min_heads))
-    if pieces == 1 and local_heads >= 2 * max(1, -(-min_heads // 2)) and local_heads > 1:
+    if split_small and pieces == 1 and local_heads >= 2 * max(1, -(-min_heads // 2)) and local_heads > 1:
         pieces = 2
     base, extra = divmod(local_heads, pieces)
     return [base] * (pieces - extra) + [base + 1] * extra
@@ -228,7 +278,8 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
     re-shards them, so the rotated tensors are never written on this rank.
     transport: "nccl" (pack, all_to_all_single, unpack), "peer" (the re-shard kernels store to and load from
     the peers' buffers over NVLink; CUDA tensors, B = 1, default attention), or None: the environment variable
-    MINDIESD_ULYSSES_TRANSPORT, else "nccl".
+    MINDIESD_ULYSSES_TRANSPORT, else "peer" where the call and the group allow it (one host, every GPU can map
+    the others' memory; the ranks decide together), else "nccl".
     profile: a dict that receives the summed CUDA-event milliseconds of the phases of this call
     ("pack", "exchange_in", "attention", "exchange_out", "unpack"); it synchronises the device.
     """
@@ -265,8 +316,8 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
     out = _out if _out is not None else torch.empty_like(q)
     outr = out.view(rows, n, d)
 
-    import os
-    transport = transport or os.environ.get("MINDIESD_ULYSSES_TRANSPORT", "nccl")
+    if transport is None:
+        transport = _default_transport(device, group, cuda and b == 1 and attn_fn is None)
     if transport not in ("nccl", "peer"):
         raise ParametersInvalid(f"transport must be 'nccl' or 'peer', but got {transport}.")
     if transport == "peer" and not (cuda and b == 1 and attn_fn is None):
@@ -281,15 +332,18 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
         shapes += [(world, rows, 3 * h, d)] * 2 + [(world, rows, h, d)] * 2  # send, recv, o_send, o_recv
     bufs = _buffers(key_, shapes, q.dtype, device)
 
-    compute = comm = None
+    compute = comm = ret = None
+    attn_streams = [None, None]
     if cuda:
         compute = torch.cuda.current_stream(device)
-        comm = _comm_stream(device)
-        comm.wait_stream(compute)  # the inputs and the buffers' previous readers
+        comm, ret, compute2 = _side_streams(device)
+        attn_streams = [compute, compute2]
+        for side in (comm, ret, compute2):
+            side.wait_stream(compute)  # the inputs and the buffers' previous readers
     timer = _Timer(profile, cuda)
 
-    def on_comm():
-        return torch.cuda.stream(comm) if cuda else _NULL
+    def on(stream):
+        return torch.cuda.stream(stream) if cuda else _NULL
 
     def record(stream):
         if not cuda:
@@ -299,9 +353,9 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
         return ev
 
     def exchange_in(c, head0):
-        """Pack piece c for every destination and start its all-to-all (communication stream)."""
+        """Pack piece c for every destination and start its all-to-all (inbound stream)."""
         send, recv = bufs[4 * c], bufs[4 * c + 1]
-        with on_comm():
+        with on(comm):
             if _piece_ready is not None:
                 _piece_ready(c, head0, sizes[c], comm)  # e.g. wait for the piece's heads to arrive from the host
             with timer.span("pack", comm):
@@ -311,7 +365,7 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
                 dist.all_to_all_single(recv, send, group=group)
             return record(comm)
 
-    def local_attention(c):
+    def local_attention(c, stream):
         h = sizes[c]
         recv, o_send = bufs[4 * c + 1], bufs[4 * c + 2]
         # recv[r] holds rank r's rows: with B == 1 the buffer already is [S, 3h, D].
@@ -322,49 +376,42 @@ def ulysses_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
             full = recv.view(world, b, s_loc, 3 * h, d).permute(1, 0, 2, 3, 4).reshape(b, world * s_loc, 3 * h, d)
             o_view = None
         qq, kk, vv = full[:, :, 0:h], full[:, :, h:2 * h], full[:, :, 2 * h:3 * h]
-        with timer.span("attention", compute):
+        with on(stream), timer.span("attention", stream):
             if attn_fn is None and o_view is not None and cuda:
                 _default_attention(qq, kk, vv, scale, out=o_view)  # straight into the return exchange's send buffer
             else:
                 o = attn_fn(qq, kk, vv, scale) if attn_fn else _default_attention(qq, kk, vv, scale)  # [B, S, h, D]
                 o_send.view(world, b, s_loc, h, d).copy_(o.reshape(b, world, s_loc, h, d).permute(1, 0, 2, 3, 4))
+        return record(stream)
 
-    def exchange_out(c):
+    def send_back(c, head0, done):
+        """Return exchange of piece c and the scatter into the caller's output (outbound stream)."""
         o_send, o_recv = bufs[4 * c + 2], bufs[4 * c + 3]
         if cuda:
-            comm.wait_event(record(compute))
-        with on_comm():
-            with timer.span("exchange_out", comm):
+            ret.wait_event(done)
+        with on(ret):
+            with timer.span("exchange_out", ret):
                 dist.all_to_all_single(o_recv, o_send, group=group)
-            return record(comm)
-
-    def unpack(c, head0, ev):
-        if cuda:
-            compute.wait_event(ev)
-        with timer.span("unpack", compute):
-            _move((outr,), bufs[4 * c + 3], rows, world, n_loc, head0, sizes[c], inverse=True)
-        if _piece_done is not None:
-            _piece_done(c, head0, sizes[c], compute)  # e.g. start the piece's copy back to the host
+            with timer.span("unpack", ret):
+                _move((outr,), o_recv, rows, world, n_loc, head0, sizes[c], inverse=True)
+            if _piece_done is not None:
+                _piece_done(c, head0, sizes[c], ret)  # e.g. start the piece's copy back to the host
 
     head0 = [sum(sizes[:c]) for c in range(len(sizes))]
     arrived = exchange_in(0, head0[0])
-    returning = None
     for c in range(len(sizes)):
         ready = arrived
         if c + 1 < len(sizes):
             arrived = exchange_in(c + 1, head0[c + 1])
+        stream = attn_streams[c % 2]
         if cuda:
-            compute.wait_event(ready)
-        local_attention(c)
-        if returning is not None:
-            unpack(*returning)
-        returning = (c, head0[c], exchange_out(c))
-    unpack(*returning)
+            stream.wait_event(ready)
+        send_back(c, head0[c], local_attention(c, stream))
     if cuda:
-        # The communication stream's last readers of q, k, v are the pack kernels, all of which the
-        # compute stream has waited for; the buffers are only touched again by the next call, which
-        # orders itself behind this one on both streams.
-        comm.wait_stream(compute)
+        # The caller's stream continues behind everything this call started; the side streams' last readers of
+        # q, k, v and of the buffers are then ordered before whatever the caller, or the next call, does.
+        for side in (attn_streams[1], ret, comm):
+            compute.wait_stream(side)
     timer.finish()
     return out
 
@@ -383,14 +430,16 @@ def _ulysses_peer(qr, kr, vr, out, outr, sizes, world, rank, rows, n_loc, d, sca
         shapes += [(world * rows, 3 * h, d), (world * rows, h, d)]  # receive buffer [S, 3h, D], output buffer [S, h, D]
     pb = _peer_buffers(key_ + ("peer",), shapes, qr.dtype, device, group)
     compute = torch.cuda.current_stream(device)
-    comm = _comm_stream(device)
-    comm.wait_stream(compute)
+    comm, ret, compute2 = _side_streams(device)
+    attn_streams = [compute, compute2]
+    for side in (comm, ret, compute2):
+        side.wait_stream(compute)
     timer = _Timer(profile, True)
     esz = qr.element_size()
     head0 = [sum(sizes[:c]) for c in range(len(sizes))]
 
-    def order_ranks(stream_name):
-        # Every rank reaches this point of its stream before any rank leaves it.
+    def order_ranks():
+        # Every rank reaches this point of the stream it is called under before any rank leaves it.
         dist.all_reduce(pb.flag, group=group)
 
     def send(c):
@@ -407,7 +456,7 @@ def _ulysses_peer(qr, kr, vr, out, outr, sizes, world, rank, rows, n_loc, d, sca
                 _cabi.ulysses_move((qr, kr, vr), ptrs, 3 * h * d, rows, world, n_loc, head0[c], h, cos=cos, sin=sin,
                                    rope_mode=mode, thread_blocks=0)
             with timer.span("exchange_in", comm):
-                order_ranks("comm")
+                order_ranks()
             ev = torch.cuda.Event()
             ev.record(comm)
             return ev
@@ -417,23 +466,30 @@ def _ulysses_peer(qr, kr, vr, out, outr, sizes, world, rank, rows, n_loc, d, sca
         ready = arrived
         if c + 1 < len(sizes):
             arrived = send(c + 1)
-        compute.wait_event(ready)
+        stream = attn_streams[c % 2]
+        stream.wait_event(ready)
         recv, o_buf = pb.local[2 * c], pb.local[2 * c + 1]
         full = recv.view(1, world * rows, 3 * h, d)
-        with timer.span("attention", compute):
+        with torch.cuda.stream(stream), timer.span("attention", stream):
             _cabi.attention(full[:, :, 0:h], full[:, :, h:2 * h], full[:, :, 2 * h:3 * h], head_first=False, scale=scale,
                             out=o_buf.view(1, world * rows, h, d))
-        with timer.span("exchange_out", compute):
-            order_ranks("compute")
-        with timer.span("unpack", compute):
-            ptrs = [pb.peer_ptr[r][2 * c + 1] + rank * rows * h * d * esz for r in range(world)]
-            _cabi.ulysses_move((outr,), ptrs, h * d, rows, world, n_loc, head0[c], h, inverse=True)
-        if piece_done is not None:
-            piece_done(c, head0[c], h, compute)
+        done = torch.cuda.Event()
+        done.record(stream)
+        ret.wait_event(done)
+        with torch.cuda.stream(ret):
+            with timer.span("exchange_out", ret):
+                order_ranks()
+            with timer.span("unpack", ret):
+                ptrs = [pb.peer_ptr[r][2 * c + 1] + rank * rows * h * d * esz for r in range(world)]
+                _cabi.ulysses_move((outr,), ptrs, h * d, rows, world, n_loc, head0[c], h, inverse=True)
+            if piece_done is not None:
+                piece_done(c, head0[c], h, ret)
     # The next call writes into the peers' receive buffers and this rank's output buffers again: it may only
     # start once every rank has finished reading them, i.e. after everyone's last scatter kernel.
-    order_ranks("compute")
-    comm.wait_stream(compute)
+    with torch.cuda.stream(ret):
+        order_ranks()
+    for side in (attn_streams[1], ret, comm):
+        compute.wait_stream(side)
     timer.finish()
     return out
 
@@ -463,6 +519,8 @@ def ulysses_attention_host(query: torch.Tensor, key: torch.Tensor, value: torch.
     if out is None:
         out = torch.empty(query.shape, dtype=query.dtype, pin_memory=True)
     n_loc = n // world
+    if head_chunks is None:
+        head_chunks = default_head_pieces(n_loc, s_loc * world, b, waves=8, split_small=True)
     sizes = _piece_sizes(head_chunks, n_loc, s_loc * world, b)
     skey = (device.index, tuple(query.shape), query.dtype)
     if skey not in _HOST_STAGING:

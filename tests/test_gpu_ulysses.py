@@ -37,7 +37,7 @@ def _worker(rank, world, port, head_chunks, result):
         shard = lambda x: x.chunk(world, dim=1)[rank].contiguous()  # noqa: E731
         checks = {}
         for rep in range(2):  # the second call reuses the persistent buffers
-            out = ulysses_attention(shard(q), shard(k), shard(v), head_chunks=head_chunks)
+            out = ulysses_attention(shard(q), shard(k), shard(v), head_chunks=head_chunks, transport="nccl")
             torch.cuda.synchronize()
             # the same kernel on the same rows and heads: only the walk order of the heads differs
             checks[f"plain{rep}"] = torch.equal(out, shard(want))
@@ -47,8 +47,13 @@ def _worker(rank, world, port, head_chunks, result):
             qr, kr = (rotary_position_embedding(x, cos, sin, mode, head_first=False) for x in (q, k))
             want_r = _cabi.attention(qr, kr, v, head_first=False)
             cs, ss = (x.chunk(world, dim=0)[rank].contiguous() for x in (cos, sin))
-            out_r = ulysses_attention(shard(q), shard(k), shard(v), head_chunks=head_chunks, rope=(cs, ss, mode))
+            out_r = ulysses_attention(shard(q), shard(k), shard(v), head_chunks=head_chunks, rope=(cs, ss, mode),
+                                      transport="nccl")
             checks[mode] = torch.equal(out_r, shard(want_r))
+        # whatever transport the ranks agree on by default, and the library's own piece sizes
+        from mindiesd.parallel import default_transport
+        checks["default_transport_named"] = default_transport() in ("nccl", "peer")
+        checks["default"] = torch.equal(ulysses_attention(shard(q), shard(k), shard(v)), shard(want))
         # operands in pinned host memory, copies pipelined with the pieces
         hq, hk, hv = (shard(x).cpu().pin_memory() for x in (q, k, v))
         for rep in range(2):

@@ -86,11 +86,16 @@ def test_ulysses_rejects_indivisible_heads():
 
 def test_default_head_pieces_keeps_pieces_large_and_the_first_small():
     from mindiesd.parallel import default_head_chunks, default_head_pieces
-    # 75 600 tokens: 296 thread blocks per head, so a piece needs four heads for eight waves
-    assert default_head_pieces(20, 75600) == [4] * 5          # 2 GPUs
-    assert default_head_pieces(10, 75600) == [5, 5]           # 4 GPUs
-    assert default_head_pieces(5, 75600) == [2, 3]            # 8 GPUs: two uneven pieces, the smaller first
-    assert default_head_pieces(3, 75600) == [3]               # too few for two pieces of four waves
+    # 75 600 tokens: 296 thread blocks per head, so a piece of twenty waves needs ten heads
+    assert default_head_pieces(20, 75600) == [10, 10]         # 2 GPUs
+    assert default_head_pieces(10, 75600) == [10]             # 4 GPUs: the exchange over NVLink is cheaper than a cut
+    assert default_head_pieces(5, 75600) == [5]               # 8 GPUs
     assert default_head_pieces(20, 4096) == [20]              # short sequences: one piece
     assert default_head_pieces(12) == [1, 1, 1, 1, 2, 2, 2, 2]  # length unknown: at most eight pieces
-    assert default_head_chunks(5, 75600) == 2 and default_head_chunks(20, 4096) == 1
+    assert default_head_chunks(20, 75600) == 2 and default_head_chunks(20, 4096) == 1
+    # the host-operand pipeline hides copies over PCIe: eight waves per piece, and two pieces where it can
+    host = dict(waves=8, split_small=True)
+    assert default_head_pieces(20, 75600, **host) == [4] * 5
+    assert default_head_pieces(10, 75600, **host) == [5, 5]
+    assert default_head_pieces(5, 75600, **host) == [2, 3]    # two uneven pieces, the smaller first
+    assert default_head_pieces(3, 75600, **host) == [3]       # too few for two pieces of four waves
