@@ -38,7 +38,7 @@ import torch  # noqa: E402
 HEAD_DIM = 128
 # DRAM bytes one launch of the dense kernel moves at the benchmark shape, from one ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture has been taken.
-DENSE_DRAM_TRAFFIC_BYTES = 3.194e9  # 319.4 MB captured at 4 heads (259.3 read + 60.1 written), scaled by 10 (traffic is per head)
+DENSE_DRAM_TRAFFIC_BYTES = 3.204e9  # 320.4 MB captured at 4 heads (259.9 read + 60.4 written), scaled by 10 (traffic is per head)
 
 
 def measured_peaks():

@@ -83,58 +83,77 @@ __device__ __forceinline__ uint4 rope_vec(uint4 own, uint4 other, const float* c
     return out;
 }
 
-// One work item = one 16-byte vector.  A thread block takes whole token rows; within a row the items are
-// numbered so that consecutive threads touch consecutive addresses on both sides: vector within a head
-// (16), head of the piece, tensor (q, k, v), rank.
-template <typename T>
-__global__ void __launch_bounds__(256) ulysses_move_kernel(const MoveParams p) {
+// One work item = one 16-byte vector.  Within a token row the items are numbered so that consecutive
+// threads touch consecutive addresses on both sides: vector within a head (16), head of the piece, tensor
+// (q, k, v), rank.  What a thread moves is the same in every row, so its item numbers are taken apart once
+// (the divisions by run-time values cost more than the copy) and the loop over the thread block's rows only
+// adds the row strides; two rows are in flight per pass when nothing is rotated.
+template <typename T, bool kRotate>
+__global__ void __launch_bounds__(256, 2) ulysses_move_kernel(const MoveParams p) {
     constexpr int kVecsPerHead = 128 / kVec;  // 16
-    constexpr int kInFlight = 4;
+    constexpr int kItems = 4;                 // items of one row a thread holds at a time
+    constexpr int kRows = kRotate ? 1 : 2;    // rows in flight per pass
     const int per_tensor = p.heads * kVecsPerHead;
     const int per_rank = p.n_src * per_tensor;
     const int per_row = per_rank * p.world;
-    for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
-        const int64_t t_row = static_cast<int64_t>(row) * p.tensor_row_stride;
-        const int64_t b_row = static_cast<int64_t>(row) * p.table_row_stride;
-        for (int base = threadIdx.x; base < per_row; base += blockDim.x * kInFlight) {
-            uint4 val[kInFlight];
-            uint4 partner[kInFlight];
-            uint8_t* dst[kInFlight];
-            int vec_of[kInFlight];  // vector index within the head, -1: no rotation
+    const int64_t t_stride = p.tensor_row_stride * 2, b_stride = p.table_row_stride * 2;  // bytes per row
+    const int64_t src_stride = p.inverse ? b_stride : t_stride, dst_stride = p.inverse ? t_stride : b_stride;
+    for (int base = threadIdx.x; base < per_row; base += blockDim.x * kItems) {
+        const uint8_t* src[kItems];
+        uint8_t* dst[kItems];
+        int vec_of[kItems];  // vector index within the head if the item is rotated, else -1
+        bool on[kItems];
 #pragma unroll
-            for (int u = 0; u < kInFlight; ++u) {
-                const int item = base + u * blockDim.x;
-                if (item >= per_row) continue;
-                const int rank = item / per_rank;
-                int r = item - rank * per_rank;
-                const int which = r / per_tensor;
-                r -= which * per_tensor;
-                const int head = r / kVecsPerHead;
-                const int vec = r % kVecsPerHead;
-                const int64_t t_off = (t_row + (rank * p.group_heads + p.head0 + head) * p.tensor_head_stride + vec * kVec) * 2;
-                const int64_t b_off = (b_row + (which * p.heads + head) * 128 + vec * kVec) * 2;
-                const bool rotate = p.rope_mode != 0 && which < 2 && !p.inverse;
-                vec_of[u] = rotate ? vec : -1;
-                if (!p.inverse) {
-                    val[u] = *reinterpret_cast<const uint4*>(p.tensor[which] + t_off);
-                    if (rotate && p.rope_mode == 1)
-                        partner[u] = *reinterpret_cast<const uint4*>(p.tensor[which] + t_off + ((vec < 8) ? 128 : -128));
-                    dst[u] = p.table[rank] + b_off;
-                } else {
-                    val[u] = *reinterpret_cast<const uint4*>(p.table[rank] + b_off);
-                    dst[u] = const_cast<uint8_t*>(p.tensor[0]) + t_off;
+        for (int u = 0; u < kItems; ++u) {
+            const int item = base + u * blockDim.x;
+            on[u] = item < per_row;
+            const int it = on[u] ? item : 0;
+            const int rank = it / per_rank;
+            int r = it - rank * per_rank;
+            const int which = r / per_tensor;
+            r -= which * per_tensor;
+            const int head = r / kVecsPerHead;
+            const int vec = r % kVecsPerHead;
+            const int64_t t_off = ((rank * p.group_heads + p.head0 + head) * p.tensor_head_stride + vec * kVec) * 2;
+            const int64_t b_off = (static_cast<int64_t>(which * p.heads + head) * 128 + vec * kVec) * 2;
+            vec_of[u] = (kRotate && which < 2) ? vec : -1;
+            if (!p.inverse) {
+                src[u] = p.tensor[which] + t_off;
+                dst[u] = p.table[rank] + b_off;
+            } else {
+                src[u] = p.table[rank] + b_off;
+                dst[u] = const_cast<uint8_t*>(p.tensor[0]) + t_off;
+            }
+        }
+        for (int row0 = blockIdx.x * kRows; row0 < p.rows; row0 += gridDim.x * kRows) {
+            uint4 val[kRows][kItems];
+            uint4 partner[kItems];
+#pragma unroll
+            for (int rr = 0; rr < kRows; ++rr) {
+                const int row = row0 + rr;
+#pragma unroll
+                for (int u = 0; u < kItems; ++u) {
+                    if (!on[u] || row >= p.rows) continue;
+                    const uint8_t* s_ptr = src[u] + row * src_stride;
+                    val[rr][u] = *reinterpret_cast<const uint4*>(s_ptr);
+                    if (kRotate && vec_of[u] >= 0 && p.rope_mode == 1)
+                        partner[u] = *reinterpret_cast<const uint4*>(s_ptr + ((vec_of[u] < 8) ? 128 : -128));
                 }
             }
 #pragma unroll
-            for (int u = 0; u < kInFlight; ++u) {
-                if (base + u * blockDim.x >= per_row) continue;
-                uint4 v = val[u];
-                if (vec_of[u] >= 0) {
-                    const float* c = p.cos + static_cast<int64_t>(row) * 128 + vec_of[u] * kVec;
-                    const float* s = p.sin + static_cast<int64_t>(row) * 128 + vec_of[u] * kVec;
-                    v = rope_vec<T>(v, partner[u], c, s, p.rope_mode, vec_of[u] >= 8);
+            for (int rr = 0; rr < kRows; ++rr) {
+                const int row = row0 + rr;
+#pragma unroll
+                for (int u = 0; u < kItems; ++u) {
+                    if (!on[u] || row >= p.rows) continue;
+                    uint4 v = val[rr][u];
+                    if (kRotate && vec_of[u] >= 0) {
+                        const float* c = p.cos + static_cast<int64_t>(row) * 128 + vec_of[u] * kVec;
+                        const float* sn = p.sin + static_cast<int64_t>(row) * 128 + vec_of[u] * kVec;
+                        v = rope_vec<T>(v, partner[u], c, sn, p.rope_mode, vec_of[u] >= 8);
+                    }
+                    *reinterpret_cast<uint4*>(dst[u] + row * dst_stride) = v;
                 }
-                *reinterpret_cast<uint4*>(dst[u]) = v;
             }
         }
     }
@@ -263,11 +282,20 @@ extern "C" int mindiesd_ulysses_move(const mindiesd_ulysses_move_args* a, void* 
     p.cos = a->cos;
     p.sin = a->sin;
     p.rope_mode = a->rope_mode;
-    // One thread block per row until every SM holds eight; more rows than that are walked in a loop.
-    const int grid = a->thread_blocks > 0 ? a->thread_blocks : (a->rows < 148 * 8 ? a->rows : 148 * 8);
+    // One thread block per pass of rows until every SM holds its two; more rows than that are walked in a loop.
+    const int rows_per_pass = a->rope_mode ? 1 : 2;
+    const int passes = (a->rows + rows_per_pass - 1) / rows_per_pass;
+    const int resident = 148 * 2;
+    const int grid = a->thread_blocks > 0 ? a->thread_blocks : (passes < resident ? passes : resident);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (a->dtype == MINDIESD_BF16) ulysses_move_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(p);
-    else ulysses_move_kernel<__half><<<grid, 256, 0, s>>>(p);
+    const bool bf16 = a->dtype == MINDIESD_BF16;
+    if (a->rope_mode) {
+        if (bf16) ulysses_move_kernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>(p);
+        else ulysses_move_kernel<__half, true><<<grid, 256, 0, s>>>(p);
+    } else {
+        if (bf16) ulysses_move_kernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>(p);
+        else ulysses_move_kernel<__half, false><<<grid, 256, 0, s>>>(p);
+    }
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? MINDIESD_OK : static_cast<int>(e);
 }

@@ -31,9 +31,10 @@ def test_withheld_copy_gives_up_cleanly_and_the_next_launch_is_correct():
     torch.cuda.synchronize()  # the kernel returned by itself: no fault, no hang
     detail = _detail()
     assert detail[0] == 101            # a bounded wait gave up
-    # ... the MMA thread's wait for a key/value block, or a softmax warp's wait for the scores that depend on
-    # it: every role times its own wait, and whichever started first reports
-    assert detail[1] in (11, 12, 17, 20, 21)
+    # ... the MMA thread's wait for a key/value block, a softmax warp's wait for the scores that depend on it, or
+    # the loader's wait for the ring slot the withheld copy never frees: every role times its own wait, they all
+    # started within microseconds of each other, and whichever runs out first reports
+    assert detail[1] in (1, 11, 12, 17, 20, 21), detail
     assert torch.isnan(out.float()).all()  # rows of a block that unwound are marked, never plausible numbers
     assert lse_probe is out
     # while the word is set, later launches leave at once and mark their rows too
