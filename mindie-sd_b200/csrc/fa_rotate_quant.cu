@@ -5,11 +5,14 @@
 // this is a GEMM that writes y (2 bytes per element) and a quantiser that reads it back; fused, y never
 // leaves the SM: 2 bytes in, 1 byte out per element.
 //
-// One CTA per (row block, head): warp 4 fetches R and the block's 128-token tiles with TMA and issues
-// eight tcgen05 MMAs (M128 N128 K16) per tile into 128 columns of tensor memory; warps 0-3 (one token
-// per thread) read the accumulators twice -- once for the block's absolute maximum, once to scale,
-// convert and store.  R is the B operand in its natural [k][n] layout (n contiguous), the layout V has
-// in the attention kernel.
+// Two forms.  128-token quantisation blocks (the layer's choice) run as a persistent pipeline, one CTA per
+// SM: R is fetched once, a loader thread keeps four 128-token tiles in flight, an MMA thread issues eight
+// tcgen05 MMAs (M128 N128 K16) per tile into one of four 128-column accumulators, and two groups of four
+// warps take alternate tiles: read the accumulator once (one token per thread, the 128 products stay in
+// registers), reduce the block's absolute maximum, scale, convert, store.  Loads, MMAs and the two
+// groups' passes overlap across tiles.  256- and 512-token blocks run one CTA per block: all of the
+// block's tiles are multiplied first and the accumulators are read twice (maximum, then conversion).
+// R is the B operand in its natural [k][n] layout (n contiguous), the layout V has in the attention kernel.
 #include "capi_common.h"
 #include "ptx_sm100.cuh"
 
@@ -206,6 +209,226 @@ __global__ void __launch_bounds__(kThreads) rotq_kernel(const __grid_constant__ 
     }
 }
 
+// OR of a predicate over the 128 threads that meet at named barrier `id` (one epilogue group).
+__device__ __forceinline__ bool group_or(int id, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.or.pred p, %2, 128, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"(static_cast<uint32_t>(pred)), "r"(id)
+        : "memory");
+    return r != 0;
+}
+
+// ---- persistent form, 128-token blocks ---------------------------------------------------------------
+constexpr int kPThreads = 320;  // warps 0-3 and 4-7: the two epilogue groups; warp 8: loader; warp 9: MMA
+constexpr int kPStages = 4;     // tiles of x in flight
+constexpr int kPAcc = 4;        // accumulators (128 columns each: all of tensor memory)
+
+template <int kFmt>
+__global__ void __launch_bounds__(kPThreads, 1) rotq_persistent_kernel(const __grid_constant__ RotqParams p, int items) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sm_r = smem;
+    uint8_t* sm_x = smem + kTileBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm_x + kPStages * kTileBytes);
+    const uint32_t bar_base = smem_u32(bars);
+    auto bar_r = [&]() { return bar_base; };
+    auto x_full = [&](int i) { return bar_base + 8u * (1 + i); };
+    auto x_empty = [&](int i) { return bar_base + 8u * (1 + kPStages + i); };
+    auto acc_full = [&](int i) { return bar_base + 8u * (1 + 2 * kPStages + i); };
+    auto acc_empty = [&](int i) { return bar_base + 8u * (1 + 2 * kPStages + kPAcc + i); };
+    auto bar_done = [&]() { return bar_base + 8u * (1 + 2 * kPStages + 2 * kPAcc); };
+    constexpr int kNumBars = 2 + 2 * kPStages + 2 * kPAcc;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* abort_site = abort_flag + 1;
+    float* warp_max = reinterpret_cast<float*>(tmem_slot + 4);  // [group][parity][warp]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // tiles of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; tile w = block + blocks * (head + heads * batch)
+    const int my_items = items > static_cast<int>(blockIdx.x) ? (items - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;
+    auto where = [&](int i, int& blk, int& head, int& batch) {
+        const int w = static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x);
+        blk = w % p.blocks;
+        const int hb = w / p.blocks;
+        head = hb % p.heads;
+        batch = hb / p.heads;
+    };
+
+    if (__syncthreads_or(tid == 0 && p.status && *reinterpret_cast<volatile int*>(p.status) != 0)) return;
+
+    if (tid == 0) {
+        mbar_init(bar_r(), 1);
+        for (int i = 0; i < kPStages; ++i) {
+            mbar_init(x_full(i), 1);
+            mbar_init(x_empty(i), 1);
+        }
+        for (int i = 0; i < kPAcc; ++i) {
+            mbar_init(acc_full(i), 1);
+            mbar_init(acc_empty(i), 128);
+        }
+        mbar_init(bar_done(), 1);
+        *abort_flag = 0;
+        *abort_site = 0;
+        fence_mbar_init();
+    }
+    if (warp == 8 && lane == 0) {
+        tma_prefetch_desc(&p.tm_x);
+        tma_prefetch_desc(&p.tm_r);
+    }
+    if (warp == 0) {
+        __syncwarp();
+        tmem_alloc(smem_u32(tmem_slot), 128 * kPAcc);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 8) {
+        // ---- loader ----
+        if (lane == 0) {
+            mbar_arrive_expect_tx(bar_r(), kTileBytes);
+            for (int a = 0; a < 2; ++a) tma_load_4d(smem_u32(sm_r + a * kAtomBytes), &p.tm_r, bar_r(), a * 64, 0, 0, 0);
+            int issued = 0;
+            for (int i = 0; i < my_items; ++i) {
+                const int s = i % kPStages;
+                if (!mbar_wait(x_empty(s), ((i / kPStages) & 1) ^ 1u, abort_flag, 1)) break;
+                int blk, head, batch;
+                where(i, blk, head, batch);
+                mbar_arrive_expect_tx(x_full(s), kTileBytes);
+                for (int a = 0; a < 2; ++a)
+                    tma_load_4d(smem_u32(sm_x + s * kTileBytes + a * kAtomBytes), &p.tm_x, x_full(s), a * 64, blk * kTile,
+                                head, batch);
+                ++issued;
+            }
+            // Every started copy is waited for before the CTA may exit.
+            mbar_wait_drain(bar_r(), 0);
+            const int pending = issued < kPStages ? issued : kPStages;
+            for (int k = 0; k < pending; ++k) {
+                const int n = issued - 1 - k;
+                mbar_wait_drain(x_full(n % kPStages), static_cast<uint32_t>(n / kPStages) & 1u);
+            }
+        }
+    } else if (warp == 9) {
+        // ---- MMA issue ----
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(kFmt, kTile, kTile, false, true);
+            const uint32_t r_lo = desc_lo(smem_u32(sm_r), kAtomBytes);  // MN-major: 16 KB between the 64-column atoms
+            bool ok = mbar_wait(bar_r(), 0, abort_flag, 2);
+            for (int i = 0; ok && i < my_items; ++i) {
+                const int s = i % kPStages, a = i % kPAcc;
+                ok = mbar_wait(x_full(s), (i / kPStages) & 1u, abort_flag, 3);
+                if (!ok) break;
+                ok = mbar_wait(acc_empty(a), ((i / kPAcc) & 1) ^ 1u, abort_flag, 4);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t x_lo = desc_lo(smem_u32(sm_x + s * kTileBytes), 16);
+#pragma unroll
+                for (int kc = 0; kc < 8; ++kc) {  // 16 channels of x = 16 rows of R per MMA
+                    const uint32_t a_off = (kc >> 2) * (kAtomBytes >> 4) + (kc & 3) * 2;
+                    const uint32_t b_off = kc * (16 * 128 >> 4);
+                    umma_ss_lohi<false>(tmem_base + a * kTile, x_lo + a_off, r_lo + b_off, kDescHiSbo1024, idesc, kc > 0);
+                }
+                umma_commit(acc_full(a));
+                umma_commit(x_empty(s));
+            }
+            // Tensor memory is freed at the end: every product issued must be over by then.
+            umma_commit(bar_done());
+            mbar_wait_drain(bar_done(), 0);
+        }
+    } else {
+        // ---- epilogue groups: tiles g, g + 2, ... ----
+        const int g = warp >> 2, wg = warp & 3;
+        const uint32_t lane_base = static_cast<uint32_t>(wg * 32) << 16;
+        for (int i = g; i < my_items; i += 2) {
+            const int a = i % kPAcc;
+            // The four warps of a group stay together: they meet at a barrier below, so a wait that gave up in
+            // one of them takes all of them out of the loop.
+            const bool gave_up = !__all_sync(0xffffffffu, mbar_wait(acc_full(a), (i / kPAcc) & 1u, abort_flag, 10 + g));
+            if (group_or(1 + g, gave_up)) break;
+            tc_fence_after();
+            uint32_t r[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(tmem_base + lane_base + a * kTile + c * 32, r[c]);
+            tmem_wait_ld();
+            // the accumulator is in registers: the MMA thread may reuse it
+            tc_fence_before();
+            mbar_arrive(acc_empty(a));
+            float m4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int j = 0; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], fabsf(__uint_as_float(r[c][j])));
+            float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            float* wm = warp_max + (g * 2 + ((i >> 1) & 1)) * 4;  // alternate buffers: the previous tile's may still be read
+            if (lane == 0) wm[wg] = mx;
+            if (g == 0) asm volatile("bar.sync 3, 128;" ::: "memory");
+            else asm volatile("bar.sync 4, 128;" ::: "memory");
+            const float amax = fmaxf(fmaxf(wm[0], wm[1]), fmaxf(wm[2], wm[3]));
+            const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+            const float inv = 1.0f / scale;
+            int blk, head, batch;
+            where(i, blk, head, batch);
+            if (wg == 0 && lane == 0) p.scales[(static_cast<int64_t>(batch) * p.heads + head) * p.blocks + blk] = scale * p.post_scale;
+            const int row = blk * kTile + wg * 32 + lane;
+            if (row < p.seq) {
+                uint4* dst = reinterpret_cast<uint4*>(p.out + ((static_cast<int64_t>(batch) * p.heads + head) * p.seq + row) * 128);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        w[j] = pack_quad_e4m3(__uint_as_float(r[c][4 * j]) * inv, __uint_as_float(r[c][4 * j + 1]) * inv,
+                                              __uint_as_float(r[c][4 * j + 2]) * inv, __uint_as_float(r[c][4 * j + 3]) * inv);
+                    dst[2 * c] = make_uint4(w[0], w[1], w[2], w[3]);
+                    dst[2 * c + 1] = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 128 * kPAcc);
+    }
+    if (tid == 0 && *abort_flag && p.status) {
+        if (atomicCAS(p.status, 0, kStatusRotqWaitGaveUp) == 0) {
+            p.status[1] = *abort_site;
+            p.status[2] = static_cast<int>(blockIdx.x);
+            p.status[3] = 0;
+            p.status[4] = 0;
+        }
+    }
+}
+
+template <int kFmt>
+cudaError_t launch_rotq_persistent(const RotqParams& p, int batch, cudaStream_t stream) {
+    const int smem = (1 + kPStages) * kTileBytes + 512 + 1024;
+    cudaError_t e = cudaFuncSetAttribute(rotq_persistent_kernel<kFmt>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    const int64_t items = static_cast<int64_t>(p.blocks) * p.heads * batch;
+    if (items > 0x7fffffff) return cudaErrorInvalidValue;
+    static const int sms = [] {
+        int dev = 0, n = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        return n > 0 ? n : 148;
+    }();
+    const int grid = items < sms ? static_cast<int>(items) : sms;
+    rotq_persistent_kernel<kFmt><<<grid, kPThreads, smem, stream>>>(p, static_cast<int>(items));
+    return cudaGetLastError();
+}
+
 template <int kFmt, int kTiles>
 cudaError_t launch_rotq(const RotqParams& p, dim3 grid, cudaStream_t stream) {
     const int smem = (1 + kTiles) * kTileBytes + 256 + 1024;
@@ -235,7 +458,7 @@ int rotate_quant_launch(const void* x, const int64_t x_stride[3], const void* ro
     const dim3 grid(p.blocks, heads, batch);
     const bool bf16 = dtype == MINDIESD_BF16;
     cudaError_t e;
-    if (row_block == 128) e = bf16 ? launch_rotq<1, 1>(p, grid, stream) : launch_rotq<0, 1>(p, grid, stream);
+    if (row_block == 128) e = bf16 ? launch_rotq_persistent<1>(p, batch, stream) : launch_rotq_persistent<0>(p, batch, stream);
     else if (row_block == 256) e = bf16 ? launch_rotq<1, 2>(p, grid, stream) : launch_rotq<0, 2>(p, grid, stream);
     else e = bf16 ? launch_rotq<1, 4>(p, grid, stream) : launch_rotq<0, 4>(p, grid, stream);
     return e == cudaSuccess ? MINDIESD_OK : static_cast<int>(e);
