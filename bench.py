@@ -8,8 +8,10 @@ torchrun, one rank per GPU) runs the same layer sequence-parallel with the Ulyss
 repeating the layer (`config.layers_per_step`) so that the timed region lasts about two seconds at
 every N; the total work per layer is fixed ("strong" scaling) and `value` is the whole job's
 dense-equivalent TFLOP/s.  Before the timed region every rank of an N > 1 run checks its Ulysses output
-bit for bit against the single-GPU kernel on the unsharded tensors (`config.parity`).  Rank 0 prints one
-JSON line.  Inputs are seeded synthetic tensors of the named shapes (no dataset exists for this path);
+bit for bit against the single-GPU kernel on the unsharded tensors (`config.parity`), and after it the
+rank's own heads are timed through the attention kernel alone in the same power state, so that
+`config.phases_of_one_layer.exposed_ms` is what the exchange costs after all overlap.  `--ulysses-pieces
+2,3` and `--ulysses-transport nccl|peer` override the library's choices.  Rank 0 prints one JSON line.  Inputs are seeded synthetic tensors of the named shapes (no dataset exists for this path);
 3.1 GB of operands per step exceed the 126 MB L2, so no L2 flush is needed between steps.
 
 Other single-GPU workloads of the same path (`--workload sparse|sparse_layer|fp8|fp8_layer|mask|quant|rotate_quant|rearrange|estimate|ada_layer|c2|ulysses_move|ulysses_move_rope`) print the
