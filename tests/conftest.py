@@ -20,6 +20,13 @@ def pytest_collection_modifyitems(config, items):
     # A GPU test on a machine without one is an error of the invocation, not a pass.
     import torch
     if torch.cuda.is_available():
+        # A kernel that never returns must not hold the machine: every GPU test gets a time limit (pytest-timeout,
+        # where it is installed and no limit was given on the command line).  The "thread" method ends the
+        # process even while the main thread sits in a CUDA call that does not return.
+        if config.pluginmanager.hasplugin("timeout") and not config.getoption("timeout", None):
+            for item in items:
+                if "gpu" in item.keywords and item.get_closest_marker("timeout") is None:
+                    item.add_marker(pytest.mark.timeout(300, method="thread"))
         return
     skip = pytest.mark.skip(reason="no CUDA device")
     for item in items:
