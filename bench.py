@@ -155,10 +155,16 @@ def cpu_attention_sample(seq, target_seconds=12.0, repeats=1):
     probe = run(1024)
     rows = int(min(seq, max(1024, 1024 * target_seconds / max(probe, 1e-6))))
     rows -= rows % 128 or 0
-    best = min(run(rows) for _ in range(repeats))
-    flops = 4.0 * rows * seq * HEAD_DIM
+    # On a box with many cores a whole head takes less than the target: then several heads are timed in a row.
+    heads = int(max(1, min(8, round(target_seconds / max(probe * rows / 1024, 1e-6))))) if rows >= seq - 127 else 1
+
+    def sample():
+        return sum(run(rows) for _ in range(heads))
+
+    best = min(sample() for _ in range(repeats))
+    flops = 4.0 * heads * rows * seq * HEAD_DIM
     return {"value": flops / best / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"1 head x {rows} query rows x {seq} keys, fp32 on bf16-rounded values, {best:.2f} s"}, best, flops
+            "sample": f"{heads} head(s) x {rows} query rows x {seq} keys, fp32 on bf16-rounded values, {best:.2f} s"}, best, flops
 
 
 WORKLOAD = "wan2.1-14b-720p dense self-attention, B1 N40 S75600 D128 (21x45x80 latent grid)"
