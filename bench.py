@@ -398,7 +398,7 @@ def dense_or_ulysses(args, rank, world, device):
                             "kernel": "fa_fwd_kernel<bf16>", "flops_per_launch": cfg.flops}
         if not args.kernel_only:
             use_all_host_cores()
-            cpu, _, _ = cpu_attention_sample(cfg.seq, target_seconds=12.0)
+            cpu, _, _ = cpu_attention_sample(cfg.seq, target_seconds=16.0)
             line["cpu_baseline"] = cpu
             if not args.no_secondary:
                 del q, k, v, out, hq, hk, hv, ho
@@ -421,7 +421,7 @@ def secondary_lines(args, device, dense_value, dense_clocks):
         if sm and dsm:
             # at equal clocks: ratio of (time x median SM MHz)
             entry["speedup_over_dense_at_equal_clocks"] = (line["value"] / sm) / (dense_value / dsm)
-        for key in ("block_density", "executed_tflop", "sparsity_arg"):
+        for key in ("block_density", "executed_tflop", "sparsity_arg", "cosine_vs_bf16_kernel_heads_0_1"):
             if key in line["config"]:
                 entry[key] = line["config"][key]
         entry["roofline_frac"] = line["roofline"]["frac"]
@@ -481,10 +481,18 @@ def single_gpu_workload(args, device):
         q8, qs = _cabi.fa_block_quant(q, 128, rotate=True)
         k8, ks = _cabi.fa_block_quant(k, 128, rotate=True)
         v8, vs = _cabi.fa_block_quant(v, per_channel=True)
+        # what quantisation costs in accuracy, on the first two heads: cosine between the FP8 output and the
+        # bf16 kernel's output on the unquantised operands (flattened over rows and channels, per head)
+        want = _cabi.attention(q[:, :2], k[:, :2], v[:, :2]).float()
         del q, k, v
         out = torch.empty(q8.shape, dtype=torch.bfloat16, device=device)
         step = lambda: _cabi.attention(q8, k8, v8, q_scale=qs, k_scale=ks, v_scale=vs, k_scale_block=128,  # noqa: E731
                                        v_scale_block=0, out=out)
+        step()
+        got = out[:, :2].float()
+        cos = torch.nn.functional.cosine_similarity(got.flatten(2), want.flatten(2), dim=-1)
+        extra = {"cosine_vs_bf16_kernel_heads_0_1": [round(x, 6) for x in cos.flatten().tolist()]}
+        del want, got
         work, unit = cfg.flops, "TFLOP/s"
         label = "FP8-e4m3 attention (operands pre-quantised), B1 N40 S75600 D128"
     elif name == "mask":
