@@ -106,15 +106,16 @@ def test_large_logits_do_not_overflow():
     _status_ok()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("jump", ["lower_half", "upper_half", "one_key_lower", "one_key_upper", "every_block"])
-def test_row_max_jumps_inside_a_key_block(jump):
+def test_row_max_jumps_inside_a_key_block(jump, dtype):
     """The running max jumps far beyond its allowed lag in the first 64 keys of a block only, in the last 64
     only, at a single key, or block after block: every way the kernel's speculative exponentials can fail
     their row-sum test and be taken again."""
     from mindiesd import _cabi
-    q = inputs.randn(63, 1, 2, 384, 128, dtype=torch.bfloat16) * 4
-    k = inputs.randn(64, 1, 2, 1280, 128, dtype=torch.bfloat16) * 4
-    v = inputs.randn(65, 1, 2, 1280, 128, dtype=torch.bfloat16)
+    q = inputs.randn(63, 1, 2, 384, 128, dtype=dtype) * 4
+    k = inputs.randn(64, 1, 2, 1280, 128, dtype=dtype) * 4
+    v = inputs.randn(65, 1, 2, 1280, 128, dtype=dtype)
     if jump == "lower_half":
         k[:, :, 512:576] *= 3
     elif jump == "upper_half":
