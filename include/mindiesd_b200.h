@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define MINDIESD_B200_ABI_VERSION 2
+#define MINDIESD_B200_ABI_VERSION 3
 
 enum {
     MINDIESD_OK = 0,
@@ -140,9 +140,41 @@ typedef struct mindiesd_attn_args {
        key block (the copy is neither started nor announced), so that the consumer's wait runs into
        wait_limit_us.  It exists to exercise the give-up path without faulting or hanging the GPU. */
     int32_t test_withhold;
+
+    /* Block-sparse attention only (sparse_mode 1 or 2), optional.  A thread block of the kernel works on two
+       128-row query blocks at once and walks the UNION of their key-block lists; the more the two lists
+       differ, the more steps serve one of the two only.  q_pairs names, per (batch, head), which two query
+       blocks share a thread block: int32 [batch, heads, q_pair_count, 2], every query block exactly once, -1
+       as the second entry of a thread block that has one only (mindiesd_rf_pair_blocks builds the table from
+       a block mask, pairing blocks whose lists overlap most).  Null: neighbouring blocks (2i, 2i+1), which is
+       what the reference's kernels do too.  The result is the same either way, bit for bit: a query row walks
+       its own key blocks in the same order whoever shares its thread block.  Measured at the 591-block
+       RainFusion mask of a 21x45x80 grid (density 0.32): 17-19 % of the steps serve one tile with neighbouring
+       blocks, 8-10 % with the table, and the launch gets 1.8 % shorter; building the table takes 0.55 ms, so it
+       pays where mask and table are kept across steps.  Not combined with causal,
+       packed sequences, e4m3 operands or perm_t without perm_inputs_permuted (MINDIESD_E_VALUE). */
+    const int32_t* q_pairs;
+    int32_t q_pair_count;
 } mindiesd_attn_args;
 
 int mindiesd_attention_fwd(const mindiesd_attn_args* args, void* stream);
+
+/*
+ * Pairs the 128-row query blocks of every (batch, head) of a block mask by the similarity of their key-block
+ * lists, for mindiesd_attn_args.q_pairs: greedy, heaviest row first, each taking the free row with the largest
+ * Jaccard overlap.  mask: int8 [batch, heads, q_blocks, kv_blocks] by element strides (non-zero = kept);
+ * pairs: int32 [batch, heads, (q_blocks + 1) / 2, 2] contiguous.  q_blocks, kv_blocks <= 1024.
+ * No counterpart in the reference (its kernels take neighbouring blocks in index order,
+ * csrc/ops/block_sparse_attention, csrc/ops/ada_block_sparse_attention).
+ */
+typedef struct mindiesd_pair_args {
+    const int8_t* mask;
+    int64_t mask_stride[3];
+    int32_t batch, heads, q_blocks, kv_blocks;
+    int32_t* pairs;
+} mindiesd_pair_args;
+
+int mindiesd_rf_pair_blocks(const mindiesd_pair_args* args, void* stream);
 
 /*
  * RainFusion token permutation of the image tokens of a (t, h, w) latent grid into 8x8 spatial

@@ -261,6 +261,14 @@ extern "C" int mindiesd_attention_fwd(const mindiesd_attn_args* a, void* stream)
         p.perm_w = a->perm_w;
         p.perm_txt = a->perm_txt;
     }
+    if (a->q_pairs) {
+        if (a->sparse_mode == MINDIESD_SPARSE_NONE || fp8 || a->causal || a->num_seqs > 0 || p.perm_on == 1)
+            return MINDIESD_E_VALUE;
+        if (a->q_pair_count != (p.q_blocks + 1) / 2) return MINDIESD_E_SHAPE;
+        if (reinterpret_cast<uintptr_t>(a->q_pairs) % 4) return MINDIESD_E_STRIDE;
+        p.q_pairs = a->q_pairs;
+        p.q_pair_count = a->q_pair_count;
+    }
     p.wait_limit_us = a->wait_limit_us ? a->wait_limit_us : kDefaultWaitLimitUs;
     p.test_withhold = a->test_withhold;
     p.status = device_status_word();

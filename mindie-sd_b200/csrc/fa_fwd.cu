@@ -200,7 +200,9 @@ __device__ __noinline__ void rare_rescale_o(uint32_t taddr_o, float alpha) {
 }  // namespace
 
 // kIn: element type of q/k/v and of the stored probabilities (0 bf16, 1 fp16, 3 e4m3).
-template <int kIn>
+// kPairs: the two query tiles of a thread block are the two 128-row blocks a table names (block-sparse
+// attention with tiles paired by the similarity of their key lists) instead of two neighbours.
+template <int kIn, bool kPairs = false>
 __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_constant__ FaParams p) {
     constexpr bool kFp8 = kIn == 3;
     constexpr bool kSplit = kFp8 || kMaxFirst;  // P is handed to the MMA thread in two parts
@@ -260,7 +262,24 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         qpair = static_cast<int>(gridDim.x) - 1 - qpair;  // the tiles with the most visible keys start first
     }
     const int q_row0 = qpair * 2 * kTile;
-    const bool tile1_valid = q_row0 + kTile < q_len;
+    // First row of each tile: two neighbouring 128-row blocks, or the two blocks the pairing table names
+    // (-1: this thread block has one tile only).
+    int pair_blk[2] = {0, 0};
+    if constexpr (kPairs) {
+        const int32_t* pr = p.q_pairs + ((static_cast<int64_t>(batch) * p.heads + head) * gridDim.x + qpair) * 2;
+        pair_blk[0] = pr[0];
+        pair_blk[1] = pr[1];
+    }
+    auto tile_row0 = [&](int t) -> int {
+        if constexpr (kPairs) return pair_blk[t] * kTile;
+        else return q_row0 + t * kTile;
+    };
+    const bool tile1_valid = kPairs ? (pair_blk[1] >= 0 && pair_blk[1] * kTile < q_len) : (q_row0 + kTile < q_len);
+    // Row of the output that thread tid < 256 answers for when its thread block does not compute (NaN marking).
+    auto marked_row = [&](int i) -> int {
+        if constexpr (kPairs) return (i < kTile || tile1_valid) ? tile_row0(i >> 7) + (i & (kTile - 1)) : q_len;
+        else return q_row0 + i;
+    };
     const int nkb = p.cu_seqlens_q ? min((k_len + kTile - 1) / kTile, kMaxKvBlocks) : p.kv_blocks;
     // Causal attention, aligned to the last query and the last key of the sequence: query i sees key j
     // iff j <= i + causal_off.  vis[t]: key blocks tile t can see at all.
@@ -268,7 +287,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     int vis[2] = {nkb, nkb};
     if (p.causal) {
         for (int t = 0; t < 2; ++t) {
-            const int last_key = q_row0 + t * kTile + kTile - 1 + causal_off;  // of the tile's last row
+            const int last_key = tile_row0(t) + kTile - 1 + causal_off;  // of the tile's last row
             vis[t] = last_key < 0 ? 0 : min(nkb, last_key / kTile + 1);
         }
     }
@@ -278,9 +297,9 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
     // The decision is taken once per thread block: all of its threads stay or all leave (the ones that stay
     // set up barriers and tensor memory for the others).  A block that leaves marks its rows.
     if (__syncthreads_or(tid == 0 && p.status && *reinterpret_cast<volatile int*>(p.status) != 0)) {
-        if (tid < 2 * kTile && q_row0 + tid < q_len)
-            poison_row(p, batch, head, q_base + (p.perm_on ? source_of(make_grid(p.perm_t, p.perm_h, p.perm_w, p.perm_txt), q_row0 + tid)
-                                                           : q_row0 + tid));
+        if (tid < 2 * kTile && marked_row(tid) < q_len)
+            poison_row(p, batch, head, q_base + (p.perm_on ? source_of(make_grid(p.perm_t, p.perm_h, p.perm_w, p.perm_txt), marked_row(tid))
+                                                           : marked_row(tid)));
         return;
     }
     const uint32_t wait_us = p.wait_limit_us;
@@ -317,15 +336,19 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         uint8_t* f0 = sm_flags;
         uint8_t* f1 = sm_flags + kMaxKvBlocks;
         const int qb0 = qpair * 2;
+        auto q_block = [&](int t) -> int {
+            if constexpr (kPairs) return pair_blk[t] >= 0 ? pair_blk[t] : pair_blk[0];
+            else return qb0 + t;
+        };
         if (p.sparse_mode == 0) {
             for (int j = tid; j < nkb; j += kThreads) {
                 f0[j] = j < vis[0];
                 f1[j] = tile1_valid && j < vis[1];
             }
         } else if (p.sparse_mode == 1) {
-            const int8_t* m0 = p.block_mask + batch * p.mask_stride[0] + head * p.mask_stride[1] +
-                               static_cast<int64_t>(qb0) * p.mask_stride[2];
-            const int8_t* m1 = m0 + p.mask_stride[2];
+            const int8_t* mh = p.block_mask + batch * p.mask_stride[0] + head * p.mask_stride[1];
+            const int8_t* m0 = mh + static_cast<int64_t>(q_block(0)) * p.mask_stride[2];
+            const int8_t* m1 = mh + static_cast<int64_t>(q_block(1)) * p.mask_stride[2];
             for (int j = tid; j < nkb; j += kThreads) {
                 f0[j] = m0[j] != 0 && j < vis[0];
                 f1[j] = tile1_valid && m1[j] != 0 && j < vis[1];
@@ -337,7 +360,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             }
             __syncthreads();
             for (int t = 0; t < (tile1_valid ? 2 : 1); ++t) {
-                const int64_t row = static_cast<int64_t>(qb0 + t) * p.heads + head;
+                const int64_t row = static_cast<int64_t>(q_block(t)) * p.heads + head;
                 const int64_t* ids = p.select_idx + row * p.select_stride;
                 int64_t n = p.select_num[row];
                 if (n > nkb) n = nkb;
@@ -379,7 +402,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             __syncwarp();
             for (int t = 0; t < (tile1_valid ? 2 : 1); ++t)
                 tma_load_4d(smem_u32(sm_q + t * C::kTileBytes) + my_off, &p.tm_q8, bar_q(), atom * C::kBoxInner,
-                            group_token(q_row0 + t * kTile + grp * 8, q_len), head, batch);
+                            group_token(tile_row0(t) + grp * 8, q_len), head, batch);
             Ring ring;
             int issued = 0;
             bool ok = true;
@@ -412,7 +435,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
             for (int t = 0; t < (tile1_valid ? 2 : 1); ++t)
                 for (int a = 0; a < C::kAtoms; ++a)
                     tma_load_4d(smem_u32(sm_q + t * C::kTileBytes + a * C::kAtomBytes), &p.tm_q, bar_q(),
-                                a * C::kBoxInner, q_base + q_row0 + t * kTile, head, batch);
+                                a * C::kBoxInner, q_base + tile_row0(t), head, batch);
             Ring ring;
             int issued = 0, withheld = -1;
             bool ok = true;
@@ -569,13 +592,13 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         // ---- softmax, O rescale, epilogue: one query row per thread ------------------------------
         const int t = warp >> 2;  // tile of this warpgroup
         const int row_in_tile = tid & (kTile - 1);
-        const int q_row = q_row0 + t * kTile + row_in_tile;
+        const int q_row = tile_row0(t) + row_in_tile;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t taddr_s = tmem_base + (t ? kColS1 : kColS0) + lane_base;
         const uint32_t taddr_o = tmem_base + (t ? kColO1 : kColO0) + lane_base;
         const uint8_t* my_flags = t ? f1 : f0;
         const int tail_valid = k_len - (nkb - 1) * kTile;  // valid columns of the last kv block
-        const int tile_last_key = q_row0 + t * kTile + causal_off;  // last key the tile's FIRST row sees
+        const int tile_last_key = tile_row0(t) + causal_off;  // last key the tile's FIRST row sees
         // The running max may lag the true max by this much (log2 units) before O is rescaled; the
         // probabilities then reach 2^lag, which two-byte formats hold but e4m3 does not.
         constexpr float kLag = kFp8 ? kFp8Lag : kRescaleThreshold;
@@ -587,7 +610,7 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         const float* k_sc = nullptr;
         const float* v_blk = nullptr;
         if constexpr (kFp8) {
-            int qb = q_row0 / kTile + t;
+            int qb = tile_row0(t) / kTile;
             if (qb >= p.q_blocks) qb = p.q_blocks - 1;
             q_sc = p.q_scale[(static_cast<int64_t>(batch) * p.heads + head) * p.q_blocks + qb];
             k_sc = p.k_scale + (static_cast<int64_t>(batch) * p.kv_heads + kv_head) * p.k_scale_count;
@@ -985,9 +1008,9 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
-    if (*abort_flag && tid < 2 * kTile && q_row0 + tid < q_len)
-        poison_row(p, batch, head, q_base + (p.perm_on ? source_of(make_grid(p.perm_t, p.perm_h, p.perm_w, p.perm_txt), q_row0 + tid)
-                                                       : q_row0 + tid));
+    if (*abort_flag && tid < 2 * kTile && marked_row(tid) < q_len)
+        poison_row(p, batch, head, q_base + (p.perm_on ? source_of(make_grid(p.perm_t, p.perm_h, p.perm_w, p.perm_txt), marked_row(tid))
+                                                       : marked_row(tid)));
     if (tid == 0 && *abort_flag && p.status) {
         // First CTA to report wins the word and leaves where it stopped behind it.
         if (atomicCAS(p.status, 0, kStatusFaWaitGaveUp) == 0) {
@@ -1001,19 +1024,25 @@ __global__ void __launch_bounds__(kThreads, 1) fa_fwd_kernel(const __grid_consta
 
 int fa_fwd_smem_bytes(bool fp8) { return (fp8 ? Cfg<true>::kSmemBytes : Cfg<false>::kSmemBytes) + 1024; }
 
-template <int kIn>
+template <int kIn, bool kPairs = false>
 static cudaError_t launch_one(const FaParams& p, cudaStream_t stream) {
     const int smem = fa_fwd_smem_bytes(kIn == 3);
-    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<kIn>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<kIn, kPairs>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     // Packed sequences: every sequence rounds its tile pairs up, so seq_q / 256 + num_seqs bounds their number.
-    const int pairs = p.cu_seqlens_q ? p.seq_q / (2 * kTile) + p.num_seqs : (p.seq_q + 2 * kTile - 1) / (2 * kTile);
+    const int pairs = kPairs ? p.q_pair_count
+                             : (p.cu_seqlens_q ? p.seq_q / (2 * kTile) + p.num_seqs : (p.seq_q + 2 * kTile - 1) / (2 * kTile));
     dim3 grid(pairs, p.heads, p.batch);
-    fa_fwd_kernel<kIn><<<grid, kThreads, smem, stream>>>(p);
+    fa_fwd_kernel<kIn, kPairs><<<grid, kThreads, smem, stream>>>(p);
     return cudaGetLastError();
 }
 
 cudaError_t fa_fwd_launch(const FaParams& p, cudaStream_t stream) {
+    if (p.q_pairs) {  // the caller checked: block mask or lists, two-byte operands, no causal mask, no packed sequences
+        if (p.in_dtype == 0) return launch_one<0, true>(p, stream);
+        if (p.in_dtype == 1) return launch_one<1, true>(p, stream);
+        return cudaErrorInvalidValue;
+    }
     switch (p.in_dtype) {
         case 0: return launch_one<0>(p, stream);
         case 1: return launch_one<1>(p, stream);

@@ -59,6 +59,10 @@ struct FaParams {
     int* status;
     uint32_t wait_limit_us;  // time limit of every bounded wait of this launch
     int test_withhold;       // failure injection for tests: the loader withholds its first copy
+    // [B, N, grid.x, 2] 128-row query blocks of each thread block's two tiles (second -1: none), or null:
+    // neighbouring blocks.  With it the launch has q_pair_count thread blocks per head.
+    const int32_t* q_pairs;
+    int q_pair_count;
 };
 
 int fa_fwd_smem_bytes(bool fp8);

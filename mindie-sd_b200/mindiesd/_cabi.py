@@ -51,6 +51,15 @@ class AttnArgs(C.Structure):
         ("perm_t", C.c_int32), ("perm_h", C.c_int32), ("perm_w", C.c_int32), ("perm_txt", C.c_int32),
         ("perm_inputs_permuted", C.c_int32),
         ("wait_limit_us", C.c_uint32), ("test_withhold", C.c_int32),
+        ("q_pairs", C.c_void_p), ("q_pair_count", C.c_int32),
+    ]
+
+
+class PairArgs(C.Structure):
+    _fields_ = [
+        ("mask", C.c_void_p), ("mask_stride", C.c_int64 * 3),
+        ("batch", C.c_int32), ("heads", C.c_int32), ("q_blocks", C.c_int32), ("kv_blocks", C.c_int32),
+        ("pairs", C.c_void_p),
     ]
 
 
@@ -249,7 +258,7 @@ def _dims(x, head_first):
 def attention(q, k, v, head_first=True, scale=None, block_mask=None, select_idx=None, select_num=None,
               out_dtype=None, want_lse=False, q_scale=None, k_scale=None, v_scale=None, k_scale_block=0,
               v_scale_block=0, out=None, causal=False, cu_seqlens_q=None, cu_seqlens_kv=None, wait_limit_us=0,
-              test_withhold=0, perm_grid=None, perm_txt=0, perm_inputs_permuted=False):
+              test_withhold=0, perm_grid=None, perm_txt=0, perm_inputs_permuted=False, q_pairs=None):
     """mindiesd_attention_fwd on the current stream.  Returns out, or (out, lse) when want_lse.
     cu_seqlens_q / cu_seqlens_kv (int32 device tensors [num_seqs + 1]) select the packed
     variable-length form: q, k, v are then [1, N, T, D] (head_first) or [1, T, N, D]."""
@@ -294,8 +303,25 @@ def attention(q, k, v, head_first=True, scale=None, block_mask=None, select_idx=
         a.perm_txt = int(perm_txt)
         a.perm_inputs_permuted = int(bool(perm_inputs_permuted))
     a.wait_limit_us, a.test_withhold = int(wait_limit_us), int(test_withhold)
+    if q_pairs is not None:  # which two query blocks share a thread block (rf_pair_blocks)
+        if q_pairs.dtype != torch.int32 or q_pairs.device != q.device or not q_pairs.is_contiguous():
+            raise NativeLibraryError("q_pairs must be a contiguous int32 tensor on the device of q")
+        a.q_pairs, a.q_pair_count = q_pairs.data_ptr(), q_pairs.shape[-2]
     check(lib().mindiesd_attention_fwd(C.byref(a), current_stream_ptr(q.device)), "mindiesd_attention_fwd")
     return (out, lse) if want_lse else out
+
+
+def rf_pair_blocks(block_mask):
+    """mindiesd_rf_pair_blocks: int32 [B, N, (q_blocks + 1) // 2, 2] pairing of the query blocks of an int8 block
+    mask [B, N, q_blocks, kv_blocks] by the overlap of their key-block lists, for attention(q_pairs=...)."""
+    b, n, qb, kb = block_mask.shape
+    pairs = torch.empty(b, n, (qb + 1) // 2, 2, dtype=torch.int32, device=block_mask.device)
+    a = PairArgs()
+    a.mask, a.pairs = block_mask.data_ptr(), pairs.data_ptr()
+    a.mask_stride[:] = (block_mask.stride(0), block_mask.stride(1), block_mask.stride(2))
+    a.batch, a.heads, a.q_blocks, a.kv_blocks = b, n, qb, kb
+    check(lib().mindiesd_rf_pair_blocks(C.byref(a), current_stream_ptr(block_mask.device)), "mindiesd_rf_pair_blocks")
+    return pairs
 
 
 def rf_rearrange(x, grid, txt_len=0, head_first=True, inverse=False):

@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in include/mindiesd_b200.h but not exported"
     lib.mindiesd_abi_version.restype = ctypes.c_int
-    assert lib.mindiesd_abi_version() == 2
+    assert lib.mindiesd_abi_version() == 3
 
 
 def test_struct_layouts_match_the_header(tmp_path):
@@ -38,7 +38,8 @@ def test_struct_layouts_match_the_header(tmp_path):
     structs = {"mindiesd_attn_args": _cabi.AttnArgs, "mindiesd_rearrange_args": _cabi.RearrangeArgs,
                "mindiesd_mask_args": _cabi.MaskArgs, "mindiesd_pool_args": _cabi.PoolArgs,
                "mindiesd_pooled_mask_args": _cabi.PooledMaskArgs, "mindiesd_quant_args": _cabi.QuantArgs,
-               "mindiesd_estimate_args": _cabi.EstimateArgs, "mindiesd_rotate_quant_args": _cabi.RotateQuantArgs}
+               "mindiesd_estimate_args": _cabi.EstimateArgs, "mindiesd_rotate_quant_args": _cabi.RotateQuantArgs,
+               "mindiesd_pair_args": _cabi.PairArgs}
     src = tmp_path / "sz.c"
     body = "".join(f'printf("{n} %zu\\n", sizeof({n}));' for n in structs)
     src.write_text(f'#include <stdio.h>\n#include "mindiesd_b200.h"\nint main(void){{{body}return 0;}}\n')

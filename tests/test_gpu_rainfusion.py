@@ -193,6 +193,85 @@ def test_full_mask_equals_dense():
     assert torch.equal(_cabi.attention(q, k, v, block_mask=mask), _cabi.attention(q, k, v))
 
 
+def _pairs_are_a_matching(pairs, q_blocks):
+    flat = pairs.reshape(-1).tolist()
+    used = sorted(x for x in flat if x >= 0)
+    assert used == list(range(q_blocks)), "every query block exactly once"
+    assert flat.count(-1) == q_blocks % 2 and all(p[0] >= 0 for p in pairs.tolist())
+
+
+@pytest.mark.parametrize("q_blocks", [9, 16])
+def test_paired_query_blocks_give_the_same_bits(q_blocks):
+    """Query blocks paired by the overlap of their key lists (mindiesd_rf_pair_blocks) instead of by index: the
+    table is a perfect matching, and the attention output does not change by a bit -- for a block mask and for
+    the lists made from it, with a ragged tail, bf16 and fp16."""
+    from mindiesd import _cabi
+    s_q = q_blocks * 128 - 37
+    kv_blocks = 11
+    s_kv = kv_blocks * 128 - 5
+    gen = torch.Generator().manual_seed(7)
+    mask = (torch.rand(1, 3, q_blocks, kv_blocks, generator=gen) < 0.4).to(torch.int8)
+    mask[..., 0] = 1  # no empty row
+    mask[:, :, 1] = mask[:, :, q_blocks - 2]  # far-apart rows with identical lists: the pairing should find them
+    mask = mask.cuda()
+    pairs = _cabi.rf_pair_blocks(mask)
+    assert pairs.shape == (1, 3, (q_blocks + 1) // 2, 2)
+    for h in range(3):
+        _pairs_are_a_matching(pairs[0, h].cpu(), q_blocks)
+    hit = [sorted(p) == [1, q_blocks - 2] for h in range(3) for p in pairs[0, h].cpu().tolist()]
+    assert sum(hit) >= 2  # (a row may have been taken by an even closer partner in one head)
+    for dtype in (torch.bfloat16, torch.float16):
+        q = inputs.randn(90, 1, 3, s_q, 128, dtype=dtype).cuda()
+        k, v = (inputs.randn(91 + i, 1, 3, s_kv, 128, dtype=dtype).cuda() for i in range(2))
+        plain, lse0 = _cabi.attention(q, k, v, block_mask=mask, want_lse=True)
+        paired, lse1 = _cabi.attention(q, k, v, block_mask=mask, q_pairs=pairs, want_lse=True)
+        assert torch.equal(plain, paired) and torch.equal(lse0, lse1)
+        idx, num = orf.select_lists(mask.cpu())  # the same blocks as compacted lists
+        listed = _cabi.attention(q, k, v, select_idx=idx.cuda(), select_num=num.cuda(), q_pairs=pairs)
+        assert torch.equal(plain, listed)
+    assert _cabi.device_status() == 0
+
+
+def test_pairing_is_refused_where_it_does_not_apply():
+    from mindiesd import _cabi
+    q, k, v = (inputs.randn(95 + i, 1, 1, 512, 128, dtype=torch.bfloat16).cuda() for i in range(3))
+    mask = torch.ones(1, 1, 4, 4, dtype=torch.int8, device="cuda")
+    pairs = _cabi.rf_pair_blocks(mask)
+    with pytest.raises(_cabi.NativeLibraryError):
+        _cabi.attention(q, k, v, q_pairs=pairs)  # dense: nothing to pair
+    with pytest.raises(_cabi.NativeLibraryError):
+        _cabi.attention(q, k, v, block_mask=mask, q_pairs=pairs, causal=True)
+    with pytest.raises(_cabi.NativeLibraryError):
+        _cabi.attention(q, k, v, block_mask=mask, q_pairs=pairs[:, :, :1].contiguous())  # wrong count
+
+
+def test_wan_720p_pairing_cuts_the_steps_that_serve_one_tile():
+    """The 21x45x80 RainFusion mask (2 heads): neighbouring query blocks share about four fifths of their key
+    lists; paired by overlap, the steps a thread block takes (the union of its two lists) drop by a few
+    per cent, and the layer operator, which pairs by itself, returns what the unpaired launch returns."""
+    import workloads
+    from mindiesd import _cabi
+    grid = workloads.C3.grid
+    q, k, v = workloads.make_qkv(workloads.C3, "cuda", seed=4, heads=2)
+    mask = _cabi.rf_block_mask(q, k, grid, 0, 0.75, True)
+    pairs = _cabi.rf_pair_blocks(mask)
+    m = mask[0].bool().cpu()
+    for h in range(2):
+        pr = pairs[0, h].cpu()
+        _pairs_are_a_matching(pr, 591)
+        steps_paired = sum(int((m[h, a] | (m[h, b] if b >= 0 else m[h, a])).sum()) for a, b in pr.tolist())
+        steps_index = sum(int((m[h, 2 * i] | m[h, min(2 * i + 1, 590)]).sum()) for i in range(296))
+        assert steps_paired < 0.98 * steps_index, (steps_paired, steps_index)
+    qp, kp, vp = (_cabi.rf_rearrange(x, grid, 0, True) for x in (q, k, v))
+    plain = _cabi.attention(qp, kp, vp, block_mask=mask)
+    paired = _cabi.attention(qp, kp, vp, block_mask=mask, q_pairs=pairs)
+    assert torch.equal(plain, paired)
+    import mindiesd  # noqa: F401  (registers torch.ops.mindiesd)
+    via_op = torch.ops.mindiesd.rf_sparse_attention(qp, kp, vp, mask, None, None, list(grid), 0, 128 ** -0.5, "BNSD", True)
+    assert torch.equal(via_op, _cabi.rf_rearrange(plain, grid, 0, True, inverse=True))
+    assert _cabi.device_status() == 0
+
+
 def test_wan_720p_mask_density():
     """Config C3 grid (21x45x80, 591 blocks), sparsity 0.75, on 2 heads generated on the device:
     every row keeps at least ceil(591/4) = 148 blocks plus the 29 first-frame columns, and the
