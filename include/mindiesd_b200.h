@@ -150,8 +150,8 @@ typedef struct mindiesd_attn_args {
        what the reference's kernels do too.  The result is the same either way, bit for bit: a query row walks
        its own key blocks in the same order whoever shares its thread block.  Measured at the 591-block
        RainFusion mask of a 21x45x80 grid (density 0.32): 17-19 % of the steps serve one tile with neighbouring
-       blocks, 8-10 % with the table, and the launch gets 1.8 % shorter; building the table takes 0.55 ms, so it
-       pays where mask and table are kept across steps.  Not combined with causal,
+       blocks, 8-10 % with the table, and the launch gets 0.2-1.8 % shorter (two runs); building the table takes
+       0.6 ms, so it pays, if at all, where mask and table are kept across steps.  Not combined with causal,
        packed sequences, e4m3 operands or perm_t without perm_inputs_permuted (MINDIESD_E_VALUE). */
     const int32_t* q_pairs;
     int32_t q_pair_count;

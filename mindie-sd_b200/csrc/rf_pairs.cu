@@ -31,24 +31,22 @@ __global__ void __launch_bounds__(kPairThreads) rf_pair_kernel(const PairParams 
     int* count = reinterpret_cast<int*>(bits + p.q_blocks * words);  // [q_blocks] kept blocks of a row
     int* order = count + p.q_blocks;                             // [q_blocks] rows, heaviest first
     int* free_row = order + p.q_blocks;                          // [q_blocks] 1 while unpaired
-    __shared__ unsigned long long best[kPairThreads / 32];
+    constexpr int kWarps = kPairThreads / 32;
+    __shared__ unsigned long long best[2][kWarps];               // per warp, double-buffered over the steps
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int head = blockIdx.x, batch = blockIdx.y;
     const int8_t* m = p.mask + batch * p.stride[0] + head * p.stride[1];
 
-    // bitmaps: one warp per row, a lane per word
-    for (int r = warp; r < p.q_blocks; r += kPairThreads / 32) {
+    // bitmaps: one warp per row, 32 consecutive mask bytes per load, one ballot per word
+    for (int r = warp; r < p.q_blocks; r += kWarps) {
+        const int8_t* row = m + r * p.stride[2];
         int c = 0;
-        for (int w = lane; w < words; w += 32) {
-            uint32_t v = 0;
-            for (int b = 0; b < 32; ++b) {
-                const int j = w * 32 + b;
-                if (j < p.kv_blocks && m[r * p.stride[2] + j] != 0) v |= 1u << b;
-            }
-            bits[r * words + w] = v;
+        for (int w = 0; w < words; ++w) {
+            const int j = w * 32 + lane;
+            const uint32_t v = __ballot_sync(0xffffffffu, j < p.kv_blocks && row[j] != 0);
+            if (lane == 0) bits[r * words + w] = v;
             c += __popc(v);
         }
-        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
         if (lane == 0) {
             count[r] = c;
             free_row[r] = 1;
@@ -68,38 +66,43 @@ __global__ void __launch_bounds__(kPairThreads) rf_pair_kernel(const PairParams 
     int made = 0;
     for (int k = 0; k < p.q_blocks; ++k) {
         const int a = order[k];
-        if (!free_row[a]) continue;  // uniform: shared memory, read after a barrier
-        // every thread scores the free rows it owns against row a; key = (overlap as a 32-bit fixed-point
-        // fraction, then lower index wins): Jaccard = inter / (ca + cb - inter)
+        if (!free_row[a]) continue;  // uniform: every thread wrote the same updates itself
+        // key of a candidate: Jaccard overlap inter / (ca + cb - inter) as the bits of a non-negative float
+        // (they order like the floats), then the lower index; bit 63 marks "there is a candidate"
         unsigned long long mine = 0;
         const int ca = count[a];
+        const uint32_t* ra = bits + a * words;
         for (int b = tid; b < p.q_blocks; b += kPairThreads) {
             if (b == a || !free_row[b]) continue;
+            const uint32_t* rb = bits + b * words;
             int inter = 0;
-            for (int w = 0; w < words; ++w) inter += __popc(bits[a * words + w] & bits[b * words + w]);
+            for (int w = 0; w < words; ++w) inter += __popc(ra[w] & rb[w]);
             const int uni = ca + count[b] - inter;
-            // 22 fraction bits order any two fractions with denominators <= 2048 correctly (they differ by at
-            // least 1 / 2048^2 = 2^-22 when they differ at all)
-            const unsigned long long frac = uni > 0 ? (static_cast<unsigned long long>(inter) << 22) / uni : 0ull;
-            const unsigned long long key = (frac << 32) | static_cast<unsigned>(0x7fffffff - b) | (1ull << 63);
+            const float frac = uni > 0 ? __fdividef(static_cast<float>(inter), static_cast<float>(uni)) : 0.0f;
+            const unsigned long long key = (static_cast<unsigned long long>(__float_as_uint(frac)) << 31) |
+                                           static_cast<unsigned>(0x7fffffff - b) | (1ull << 63);
             mine = key > mine ? key : mine;
         }
         for (int o = 16; o > 0; o >>= 1) {
             const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, o);
             mine = other > mine ? other : mine;
         }
-        if (lane == 0) best[warp] = mine;
+        const int buf = made & 1;
+        if (lane == 0) best[buf][warp] = mine;
         __syncthreads();
+        // every thread reduces the warps' candidates by itself: one barrier per step
+        unsigned long long top = 0;
+        for (int w = 0; w < kWarps; ++w) top = best[buf][w] > top ? best[buf][w] : top;
+        const int b = top ? 0x7fffffff - static_cast<int>(top & 0x7fffffffu) : -1;
         if (tid == 0) {
-            unsigned long long top = 0;
-            for (int w = 0; w < kPairThreads / 32; ++w) top = best[w] > top ? best[w] : top;
-            const int b = top ? 0x7fffffff - static_cast<int>(top & 0xffffffffu) : -1;
-            free_row[a] = 0;
-            if (b >= 0) free_row[b] = 0;
             out[2 * made] = a;
             out[2 * made + 1] = b;
         }
-        __syncthreads();
+        // The rows leave the free list.  Every thread came to the same (a, b) and writes the same two zeros, and
+        // a thread reads the list after its own writes: no second barrier is needed (the candidates' buffer
+        // alternates, so a thread that runs ahead does not overwrite what a slower one still reads).
+        free_row[a] = 0;
+        if (b >= 0) free_row[b] = 0;
         ++made;
     }
 }

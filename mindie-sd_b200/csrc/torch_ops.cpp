@@ -152,9 +152,9 @@ void run_attention(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v
     c10::cuda::CUDAGuard guard(q.device());
     // Block mask, MINDIESD_PAIR_BLOCKS=1: the query blocks that share a thread block are chosen by the overlap
     // of their key-block lists (fewer steps that serve only one of the two); same result bit for bit.  Off by
-    // default: at the 591-block RainFusion mask the attention gets 0.64 ms (1.8 %) shorter and building the
-    // table costs 0.55 ms, so it pays only where the caller keeps mask and table across steps (the C ABI
-    // takes a ready table: mindiesd_attn_args.q_pairs).
+    // default: at the 591-block RainFusion mask the attention gets 0.1-0.6 ms (0.2-1.8 %) shorter and building
+    // the table costs 0.6 ms, so it can pay only where the caller keeps mask and table across steps (the C
+    // ABI takes a ready table: mindiesd_attn_args.q_pairs).
     at::Tensor pairs;
     static const bool pair_blocks = [] {
         const char* e = std::getenv("MINDIESD_PAIR_BLOCKS");
