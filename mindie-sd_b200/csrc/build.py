@@ -1,12 +1,16 @@
 """Builds the native libraries of this package in-tree with nvcc for sm_100a.
 
     python mindie-sd_b200/csrc/build.py [--force] [--no-torch-ext]
+    python mindie-sd_b200/csrc/build.py --variant /tmp/libvariant.so -D SDB_FA_BF16_MODE=5 [-D ...]
 
 Outputs (next to the Python package, where its loader looks for them):
     mindiesd/plugin/libmindiesd_b200.so    the C-ABI library (CUDA only, no torch types)
     mindiesd/plugin/libPTAExtensionOPS.so  the torch operator library registering torch.ops.mindiesd.*
 The second keeps the file name the reference's loader opens
 (mindiesd/layers/register_ops.py:24-44 of MindIE-SD).
+
+--variant builds one more copy of the C-ABI library with the attention kernel's build-time switches (the -D names at
+the top of fa_fwd.cu) set differently, for compare_builds.py; the product libraries are not touched.
 """
 from __future__ import annotations
 
@@ -100,6 +104,23 @@ def build_torch_ext(force: bool = False) -> Path:
     return TORCH_EXT_LIB
 
 
+def build_variant(out: Path, defines, verbose: bool = False) -> Path:
+    """The C-ABI library with fa_fwd.cu recompiled under the given -D switches; every other object is the
+    product's (built first if needed)."""
+    build_cabi(False, False)
+    obj = Path(str(out) + ".fa_fwd.o")
+    cmd = [_nvcc()] + ARCH_FLAGS + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-D" + d for d in defines] + \
+          ["-I", str(INCLUDE), "-c", str(CSRC / "fa_fwd.cu"), "-o", str(obj)]
+    log = _run(cmd)
+    if verbose and log.strip():
+        print(log)
+    others = [str(OBJ / (p.name + ".o")) for p in sorted(CSRC.glob("*.cu")) if p.name != "fa_fwd.cu"]
+    _run([_nvcc()] + ARCH_FLAGS + ["-shared", "-cudart", "shared", "-o", str(out), str(obj)] + others +
+         ["-Xlinker", "-rpath,/usr/local/cuda/lib64"])
+    obj.unlink()
+    return out
+
+
 def build_all(force: bool = False, torch_ext: bool = True, verbose: bool = False):
     libs = [build_cabi(force, verbose)]
     if torch_ext and all((CSRC / s).exists() for s in TORCH_EXT_SOURCES):
@@ -112,7 +133,12 @@ if __name__ == "__main__":
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--no-torch-ext", action="store_true")
     ap.add_argument("-v", "--verbose", action="store_true")
+    ap.add_argument("--variant", metavar="OUT.so", help="build a copy of the C-ABI library with other switches")
+    ap.add_argument("-D", dest="defines", action="append", default=[], metavar="NAME=VALUE")
     a = ap.parse_args()
+    if a.variant:
+        print(build_variant(Path(a.variant), a.defines, a.verbose))
+        sys.exit(0)
     for lib in build_all(a.force, not a.no_torch_ext, a.verbose):
         print(lib)
     sys.exit(0)
