@@ -82,6 +82,18 @@ def test_invalid_arguments_return_codes_without_a_gpu():
     assert lib.mindiesd_sparse_block_estimate(ctypes.byref(e), None) == -5  # more key tokens than tokens
     e.causal = e.causal_key_tokens = 0
     assert lib.mindiesd_sparse_block_estimate_scratch_bytes(1, 40, 75600) == 4 * 9472 * (37 * 16 + 37) * 4
+    pa = _cabi.PairArgs()
+    assert lib.mindiesd_rf_pair_blocks(None, None) == -1
+    assert lib.mindiesd_rf_pair_blocks(ctypes.byref(pa), None) == -1  # NULL mask and table
+    pa.mask = pa.pairs = 4096
+    pa.batch = pa.heads = pa.kv_blocks = 1
+    assert lib.mindiesd_rf_pair_blocks(ctypes.byref(pa), None) == -2  # no query blocks
+    pa.q_blocks, pa.kv_blocks = 8, 2000
+    assert lib.mindiesd_rf_pair_blocks(ctypes.byref(pa), None) < 0    # beyond the capacity of one thread block
+    mv = _cabi.UlyssesMoveArgs()
+    assert lib.mindiesd_ulysses_move(ctypes.byref(mv), None) < 0
+    ro = _cabi.RopeArgs()
+    assert lib.mindiesd_rope(ctypes.byref(ro), None) == -1
     with pytest.raises(_cabi.NativeLibraryError):
         _cabi.check(-2, "x")
 
