@@ -1,9 +1,35 @@
 """`AttentionParam`: the shape key of one attention call (mindiesd/layers/flash_attn/common.py:20-61
 of MindIE-SD).  The reference uses it to cache the operator its runtime search picked; here there
-is one kernel, so it only carries the validated shape."""
+is one kernel, so it only carries the validated shape.  `lru_cache_by_attn_param` and `attn_cache` (:20-42 there)
+are kept for callers that memoise their own per-shape decisions with them."""
+import functools
+from collections import OrderedDict
 from dataclasses import dataclass
 
 import torch
+
+# One process-wide table, most recently used last; keys are AttentionParam.to_hash().
+attn_cache = OrderedDict()
+
+
+def lru_cache_by_attn_param(maxsize=None):
+    """Decorator for functions whose first argument is an AttentionParam: the result is remembered per shape in
+    `attn_cache`; with `maxsize` the least recently used shapes are dropped once the table grows beyond it."""
+    def decorate(fn):
+        @functools.wraps(fn)
+        def remembered(attn_param, *args, **kwargs):
+            key = attn_param.to_hash()
+            try:
+                value = attn_cache[key]
+            except KeyError:
+                value = attn_cache[key] = fn(attn_param, *args, **kwargs)
+                while maxsize is not None and len(attn_cache) > maxsize:
+                    attn_cache.popitem(last=False)
+            else:
+                attn_cache.move_to_end(key)
+            return value
+        return remembered
+    return decorate
 
 
 @dataclass(frozen=True)

@@ -139,3 +139,24 @@ def test_ulysses_rejects_bad_piece_sizes_and_transports():
         _piece_sizes([2, 2], 5, 75600, 1)
     with pytest.raises(ParametersInvalid, match="adding up"):
         _piece_sizes([0, 5], 5, 75600, 1)
+
+
+def test_results_are_remembered_per_attention_shape():
+    """tests/layers/flash_attn/test_attn_lru_cache.py of MindIE-SD, plus the eviction order."""
+    from mindiesd.layers.flash_attn.common import AttentionParam, attn_cache, lru_cache_by_attn_param
+    calls = []
+
+    @lru_cache_by_attn_param(maxsize=2)
+    def pick(param):
+        calls.append(param.batch_size)
+        return "case 0" if param.batch_size > 10 else "case 1"
+
+    attn_cache.clear()
+    big = AttentionParam(20, 16, 64, 128, 128, torch.float32, False)
+    small = AttentionParam(2, 16, 64, 128, 128, torch.float32, False)
+    other = AttentionParam(3, 16, 64, 128, 128, torch.float32, True)
+    assert pick(big) == "case 0" and big.to_hash() in attn_cache and attn_cache[big.to_hash()] == "case 0"
+    assert pick(small) == "case 1" and pick(big) == "case 0" and calls == [20, 2]  # the second call of `big` was remembered
+    pick(other)  # a third shape: the least recently used one (small) goes
+    assert small.to_hash() not in attn_cache and big.to_hash() in attn_cache and len(attn_cache) == 2
+    attn_cache.clear()
