@@ -62,6 +62,7 @@ struct SparseSpec {
     const at::Tensor* mask = nullptr;
     const at::Tensor* select_idx = nullptr;
     const at::Tensor* select_num = nullptr;
+    const at::Tensor* q_pairs = nullptr;  // int32 [B, N, (q_blocks + 1) / 2, 2] from rf_pair_blocks, or none
 };
 
 // What only some operators pass on: the causal triangle, where the log-sum-exp goes, packed sequences.
@@ -161,7 +162,14 @@ void run_attention(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v
         return e && e[0] == '1';
     }();
     const int q_blocks = (a.seq_q + 127) / 128, kv_blocks = (a.seq_kv + 127) / 128;
-    if (pair_blocks && sp.mode == MINDIESD_SPARSE_MASK && !extra.causal && !extra.cu_seqlens_q && !q_scale &&
+    if (sp.q_pairs) {
+        const at::Tensor& t = *sp.q_pairs;
+        TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous() && t.dim() == 4 && t.size(0) == a.batch &&
+                        t.size(1) == a.heads && t.size(2) == (q_blocks + 1) / 2 && t.size(3) == 2,
+                    "mindiesd: q_pairs must be a contiguous CUDA int32 tensor [B, N, (q_blocks + 1) / 2, 2]");
+        a.q_pairs = t.data_ptr<int32_t>();
+        a.q_pair_count = (q_blocks + 1) / 2;
+    } else if (pair_blocks && sp.mode == MINDIESD_SPARSE_MASK && !extra.causal && !extra.cu_seqlens_q && !q_scale &&
         (extra.perm[0] == 0 || extra.perm_inputs_permuted) && q_blocks >= 16 && q_blocks <= 1024 && kv_blocks <= 1024) {
         pairs = at::empty({a.batch, a.heads, (q_blocks + 1) / 2, 2}, q.options().dtype(at::kInt));
         mindiesd_pair_args pa = {};
@@ -487,7 +495,8 @@ at::Tensor rf_sparse_attention_cuda(const at::Tensor& query, const at::Tensor& k
                                     const c10::optional<at::Tensor>& block_mask,
                                     const c10::optional<at::Tensor>& select_idx,
                                     const c10::optional<at::Tensor>& select_num_idx, at::IntArrayRef latent_shape,
-                                    int64_t txt_len, double scale, std::string input_layout, bool inputs_permuted) {
+                                    int64_t txt_len, double scale, std::string input_layout, bool inputs_permuted,
+                                    const c10::optional<at::Tensor>& q_pairs) {
     TORCH_CHECK(input_layout == "BNSD" || input_layout == "BSND", "rf_sparse_attention: input_layout must be 'BNSD' or 'BSND'");
     TORCH_CHECK(latent_shape.size() == 3, "rf_sparse_attention: latent_shape must be (t, h, w)");
     TORCH_CHECK(inputs_permuted || (latent_shape[2] % 8 == 0 && txt_len % 8 == 0 && txt_len >= 0),
@@ -514,6 +523,10 @@ at::Tensor rf_sparse_attention_cuda(const at::Tensor& query, const at::Tensor& k
         sp.select_idx = &sel;
         sp.select_num = &num;
     }
+    if (q_pairs.has_value()) {
+        TORCH_CHECK(inputs_permuted, "rf_sparse_attention: q_pairs needs q, k, v in the permuted order (inputs_permuted)");
+        sp.q_pairs = &q_pairs.value();
+    }
     AttnExtra ex;
     ex.perm[0] = static_cast<int>(latent_shape[0]);
     ex.perm[1] = static_cast<int>(latent_shape[1]);
@@ -522,6 +535,26 @@ at::Tensor rf_sparse_attention_cuda(const at::Tensor& query, const at::Tensor& k
     ex.perm_inputs_permuted = inputs_permuted;
     run_attention(query, key, value, out, nullptr, head_first, scale, sp, -1, -1, nullptr, nullptr, nullptr, 0, 0, ex);
     return out;
+}
+
+// The pairing table of a block mask (mindiesd_rf_pair_blocks), for callers that keep a mask across steps.
+at::Tensor rf_pair_blocks_cuda(const at::Tensor& block_mask) {
+    TORCH_CHECK(block_mask.is_cuda() && block_mask.scalar_type() == at::kChar && block_mask.dim() == 4 &&
+                    block_mask.stride(3) == 1,
+                "rf_pair_blocks: block_mask must be a CUDA int8 tensor [B, N, q_blocks, kv_blocks]");
+    const int64_t qb = block_mask.size(2);
+    at::Tensor pairs = at::empty({block_mask.size(0), block_mask.size(1), (qb + 1) / 2, 2}, block_mask.options().dtype(at::kInt));
+    mindiesd_pair_args pa = {};
+    pa.mask = block_mask.data_ptr<int8_t>();
+    for (int i = 0; i < 3; ++i) pa.mask_stride[i] = block_mask.stride(i);
+    pa.batch = static_cast<int32_t>(block_mask.size(0));
+    pa.heads = static_cast<int32_t>(block_mask.size(1));
+    pa.q_blocks = static_cast<int32_t>(qb);
+    pa.kv_blocks = static_cast<int32_t>(block_mask.size(3));
+    pa.pairs = pairs.data_ptr<int32_t>();
+    c10::cuda::CUDAGuard guard(block_mask.device());
+    check_rc(mindiesd_rf_pair_blocks(&pa, stream_of(block_mask)), "mindiesd_rf_pair_blocks");
+    return pairs;
 }
 
 // ---- packed variable-length sequences (TND): one launch, sequence boundaries read on the device ------------
@@ -812,7 +845,8 @@ TORCH_LIBRARY(mindiesd, m) {
     m.def(
         "rf_sparse_attention(Tensor query, Tensor key, Tensor value, Tensor? block_mask, Tensor? select_idx, "
         "Tensor? select_num_idx, int[] latent_shape, int txt_len, float scale, str input_layout, "
-        "bool inputs_permuted=False) -> Tensor");
+        "bool inputs_permuted=False, Tensor? q_pairs=None) -> Tensor");
+    m.def("rf_pair_blocks(Tensor block_mask) -> Tensor");
     m.def(
         "attention_varlen_fwd(Tensor query, Tensor key, Tensor value, Tensor cu_seqlens_q, Tensor cu_seqlens_k, "
         "float scale, bool causal=False) -> Tensor");
@@ -841,6 +875,7 @@ TORCH_LIBRARY_IMPL(mindiesd, CUDA, m) {
     m.impl("attention_fwd", &attention_fwd_cuda);
     m.impl("attention_varlen_fwd", &attention_varlen_fwd_cuda);
     m.impl("rf_sparse_attention", &rf_sparse_attention_cuda);
+    m.impl("rf_pair_blocks", &rf_pair_blocks_cuda);
     m.impl("rf_rearrange", &rf_rearrange_cuda);
     m.impl("rf_block_mask", &rf_block_mask_cuda);
     m.impl("rf_pool", &rf_pool_cuda);

@@ -137,8 +137,14 @@ def _attention_fwd_fake(query, key, value, scale, head_first, causal=False):
 
 @register_ops.register_mindie_fake_op("rf_sparse_attention")
 def _rf_sparse_attention_fake(query, key, value, block_mask, select_idx, select_num_idx, latent_shape, txt_len, scale,
-                              input_layout, inputs_permuted=False):
+                              input_layout, inputs_permuted=False, q_pairs=None):
     return query.new_empty(query.shape)
+
+
+@register_ops.register_mindie_fake_op("rf_pair_blocks")
+def _rf_pair_blocks_fake(block_mask):
+    b, n, qb, _ = block_mask.shape
+    return block_mask.new_empty((b, n, (qb + 1) // 2, 2), dtype=torch.int32)
 
 
 @register_ops.register_mindie_fake_op("attention_varlen_fwd")

@@ -24,8 +24,24 @@ def permutation_fuses(latent_shape, txt_len, dtype) -> bool:
     return latent_shape[2] % 8 == 0 and int(txt_len) % 8 == 0 and dtype in (torch.bfloat16, torch.float16)
 
 
+_PAIR_TABLES = {}  # (data_ptr, version, shape, device) of a reused block mask -> its pairing table
+
+
+def pairing_table_of(mask):
+    """The query-block pairing table of a block mask that is being REUSED (`cached_mask`): built the first time the
+    mask comes back and kept while the same, unmodified tensor keeps coming back.  Building it costs about what it
+    saves in one attention launch, so a mask used once never gets one."""
+    key = (mask.data_ptr(), mask._version, tuple(mask.shape), mask.device)
+    table = _PAIR_TABLES.get(key)
+    if table is None:
+        if len(_PAIR_TABLES) >= 8:
+            _PAIR_TABLES.pop(next(iter(_PAIR_TABLES)))
+        table = _PAIR_TABLES[key] = torch.ops.mindiesd.rf_pair_blocks(mask)
+    return table
+
+
 def permuted_block_sparse_attention(q, k, v, grid, txt_len, scale, input_layout, mask=None, select_idx=None,
-                                    select_num_idx=None, fuse_loads=False):
+                                    select_num_idx=None, fuse_loads=False, q_pairs=None):
     """Block-sparse attention in the window order of `grid` on q, k, v given in their ORIGINAL order; the
     result is in the original order too.  The kernel's epilogue writes every output row straight to its
     original position, so the inverse permutation of the reference's pipeline costs nothing.  q, k and v
@@ -38,7 +54,7 @@ def permuted_block_sparse_attention(q, k, v, grid, txt_len, scale, input_layout,
                                                       float(scale), input_layout, False)
     q_, k_, v_ = (torch.ops.mindiesd.rf_rearrange(x, grid, int(txt_len), input_layout, False) for x in (q, k, v))
     return torch.ops.mindiesd.rf_sparse_attention(q_, k_, v_, mask, select_idx, select_num_idx, grid, int(txt_len),
-                                                  float(scale), input_layout, True)
+                                                  float(scale), input_layout, True, q_pairs)
 
 
 def rain_fusion_attention_v3(query, key, value, block_sparse_mask, scale=None, head_num=None,
@@ -85,8 +101,12 @@ def bsa_sparse_attention_v3(q, k, v, latent_shape_q, latent_shape_k=None, txt_le
     else:
         new_mask = cached_mask
     if q.dtype in (torch.bfloat16, torch.float16) and k.shape == q.shape and pool_size == 128:
+        # A mask that comes back from an earlier step brings its pairing table with it (query blocks that share a
+        # thread block chosen by the overlap of their key lists: same output, fewer steps in the kernel).
+        reused = cached_mask is not None and not fuse_loads and new_mask.is_cuda and new_mask.dtype == torch.int8 \
+            and 16 <= new_mask.shape[2] <= 1024 and new_mask.shape[3] <= 1024 and new_mask.stride(3) == 1
         out = permuted_block_sparse_attention(q, k, v, grid, txt_len, scale, input_layout, mask=new_mask,
-                                              fuse_loads=fuse_loads)
+                                              fuse_loads=fuse_loads, q_pairs=pairing_table_of(new_mask) if reused else None)
         return out, new_mask
     q_, k_, v_ = do_tensor_rearrange_only(q, k, v, txt_len, latent_shape_q, latent_shape_k, input_layout)
     s_dim = 2 if input_layout == "BNSD" else 1

@@ -272,6 +272,30 @@ def test_wan_720p_pairing_cuts_the_steps_that_serve_one_tile():
     assert _cabi.device_status() == 0
 
 
+@pytest.mark.parametrize("layout", ["BNSD", "BSND"])
+def test_a_reused_mask_brings_its_pairing_table(layout):
+    """bsa_sparse_attention_v3 with `cached_mask`: the second step pairs the query blocks by overlap (the table is
+    built once for the mask that came back) and returns what the first step returned, bit for bit."""
+    from mindiesd.layers.flash_attn import sparse_flash_attn_rf_v3 as v3
+    grid, heads = (3, 32, 64), 2   # 6144 tokens: 48 query blocks
+    shape = (1, heads, 6144, 128) if layout == "BNSD" else (1, 6144, heads, 128)
+    q, k, v = (inputs.randn(120 + i, *shape, dtype=torch.bfloat16).cuda() for i in range(3))
+    v3._PAIR_TABLES.clear()
+    out1, mask = v3.bsa_sparse_attention_v3(q, k, v, grid, sparsity=0.6, input_layout=layout)
+    assert not v3._PAIR_TABLES  # a fresh mask is used as it is
+    out2, mask2 = v3.bsa_sparse_attention_v3(q, k, v, grid, sparsity=0.6, input_layout=layout, cached_mask=mask)
+    assert mask2 is mask and len(v3._PAIR_TABLES) == 1
+    table = next(iter(v3._PAIR_TABLES.values()))
+    assert table.shape == (1, heads, 24, 2)
+    for h in range(heads):
+        _pairs_are_a_matching(table[0, h].cpu(), 48)
+    assert torch.equal(out1, out2)
+    out3, _ = v3.bsa_sparse_attention_v3(q, k, v, grid, sparsity=0.6, input_layout=layout, cached_mask=mask)
+    assert len(v3._PAIR_TABLES) == 1 and torch.equal(out1, out3)  # the table is reused
+    from mindiesd import _cabi
+    assert _cabi.device_status() == 0
+
+
 def test_wan_720p_mask_density():
     """Config C3 grid (21x45x80, 591 blocks), sparsity 0.75, on 2 heads generated on the device:
     every row keeps at least ceil(591/4) = 148 blocks plus the 29 first-frame columns, and the
